@@ -74,8 +74,9 @@ class CacheManager:
         by_key: Dict[Tuple, CacheGroup] = {}
         for slot in sorted(needs):
             need = needs[slot]
-            if need.kind == "state":
+            if need.keeps_state:       # (a need of pages may name state arrays beside them)
                 self.state_needs[slot] = need
+            if need.kind == "state":
                 continue
             if need.kind != "pages":
                 raise ValueError(f"cache slot {slot}: unknown cache need kind '{need.kind}'")

@@ -21,7 +21,14 @@ class CacheView:
     group: int = -1                       # page group (index into StepContext.block_tables)
     page_size: int = 0
     pages: Dict[str, torch.Tensor] = field(default_factory=dict)   # entry name -> [pages, ..., page size, last]
-    state: Optional[torch.Tensor] = None     # [state slots, *shape]
+    state: Optional[torch.Tensor] = None     # [state slots, *shape]: the array of a need of kind "state" with a shape
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)  # named state arrays, each [state slots, *shape]
+
+    def member(self, name: str) -> "CacheView":
+        """The view of one member of a mixer whose need was put together with ``CacheNeed.merged``: the pages,
+        and the state arrays ``<name>.<array>`` under their own names (``<name>.state`` as ``state``)."""
+        own = {k[len(name) + 1:]: v for k, v in self.states.items() if k.startswith(name + ".")}
+        return CacheView(self.slot, self.group, self.page_size, self.pages, own.pop("state", None), own)
 
     @property
     def k_pages(self) -> Optional[torch.Tensor]:   # [pages, kv heads, page size, head size]
@@ -56,12 +63,21 @@ class CacheStorage:
                 per_entry[e.name] = a
             for i, slot in enumerate(g.slots):
                 self._views[slot] = CacheView(slot, g.index, ps, {n: a[i] for n, a in per_entry.items()})
+        n_slots = manager.state_slots.num_slots
         for slot, need in manager.state_needs.items():
-            sdt = dtype if need.state_dtype == "compute" else getattr(torch, need.state_dtype)
-            st = torch.zeros((manager.state_slots.num_slots,) + tuple(need.state_shape), dtype=sdt, device=device)
-            self.arrays.append(st)
-            self._states.append(st)
-            self._views[slot] = CacheView(slot, state=st)
+            view = self._views.get(slot)
+            if view is None:
+                view = self._views[slot] = CacheView(slot)
+            if need.kind == "state" and need.state_shape:
+                sdt = dtype if need.state_dtype == "compute" else getattr(torch, need.state_dtype)
+                view.state = torch.zeros((n_slots,) + tuple(need.state_shape), dtype=sdt, device=device)
+                self.arrays.append(view.state)
+                self._states.append(view.state)
+            for e in need.states:
+                st = torch.zeros((n_slots,) + tuple(e.shape), dtype=_entry_dtype(e, dtype), device=device)
+                view.states[e.name] = st
+                self.arrays.append(st)
+                self._states.append(st)
         if self._states:
             manager.admit_hooks.append(self.clear_state)
 

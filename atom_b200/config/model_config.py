@@ -7,10 +7,12 @@ constant a layer needs comes from it and nothing is hard-coded elsewhere.
 """
 from __future__ import annotations
 
+import glob
 import json
 import os
+import struct
 from dataclasses import dataclass
-from typing import Any, Dict, Tuple
+from typing import Any, Dict, Mapping, Optional, Tuple
 
 
 class ConfigError(ValueError):
@@ -57,13 +59,47 @@ class ModelConfig:
         return ()
 
 
-def config_from_dict(d: Dict[str, Any]) -> ModelConfig:
+def architecture_name(d: Dict[str, Any]) -> str:
+    """``architectures[0]``, or the single name under ``architecture``."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
+    return archs[0]
+
+
+def config_from_dict(d: Dict[str, Any], shapes: Optional[Mapping[str, Tuple[int, ...]]] = None) -> ModelConfig:
+    """shapes: the checkpoint's tensor shapes by name, for architectures that read sizes from them."""
     from atom_b200.models.registry import get_architecture
 
-    return get_architecture(archs[0]).config_from_dict(d)
+    arch = get_architecture(architecture_name(d))
+    if arch.reads_shapes:
+        return arch.config_from_dict(d, shapes)
+    return arch.config_from_dict(d)
+
+
+def checkpoint_shapes(model_dir: str) -> Dict[str, Tuple[int, ...]]:
+    """Tensor name -> shape from the headers of the folder's safetensors files (8 bytes of little-endian
+    length, then that many bytes of JSON: name -> dtype, shape, data_offsets); no tensor data is read."""
+    out: Dict[str, Tuple[int, ...]] = {}
+    for f in sorted(glob.glob(os.path.join(model_dir, "*.safetensors"))):
+        with open(f, "rb") as fh:
+            head = fh.read(8)
+            if len(head) != 8:
+                raise ConfigError(f"{f}: not a safetensors file")
+            n = struct.unpack("<Q", head)[0]
+            if n > (1 << 30):
+                raise ConfigError(f"{f}: not a safetensors file (header of {n} bytes)")
+            try:
+                meta = json.loads(fh.read(n))
+            except (UnicodeDecodeError, json.JSONDecodeError) as e:
+                raise ConfigError(f"{f}: unreadable safetensors header ({e})") from e
+        for k, v in meta.items():
+            if k != "__metadata__" and isinstance(v, dict) and "shape" in v:
+                out[k] = tuple(int(x) for x in v["shape"])
+    return out
 
 
 def load_model_config(model_dir: str) -> ModelConfig:
@@ -85,7 +121,10 @@ def load_model_config(model_dir: str) -> ModelConfig:
         if isinstance(g, dict) and g.get("eos_token_id") is not None and d.get("eos_token_id") is None:
             d = dict(d)
             d["eos_token_id"] = g["eos_token_id"]
-    return config_from_dict(d)
+    from atom_b200.models.registry import get_architecture
+
+    shapes = checkpoint_shapes(model_dir) if get_architecture(architecture_name(d)).reads_shapes else None
+    return config_from_dict(d, shapes)
 
 
 def save_model_config(cfg: ModelConfig, model_dir: str) -> None:

@@ -111,7 +111,8 @@ class ModelRunner:
             tensors = load_weights(self.model, engine_config.model, self.dtype, self.device)
         self.model.bind(tensors, self.rt)
         self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
-        self.max_model_len = min(engine_config.max_model_len or self.spec.max_position, self.spec.max_position)
+        self.max_model_len = min(engine_config.max_model_len or self.spec.default_max_len or self.spec.max_position,
+                                 self.spec.max_position)
         self.page_size = engine_config.kv_cache_block_size
 
         # Decode steps (one token per request) of these batch sizes replay a captured CUDA graph.

@@ -16,13 +16,16 @@ class Architecture:
     name: str
     config_from_dict: Callable[[Dict[str, Any]], ModelConfig]
     build_spec: Callable[[ModelConfig], ModelSpec]
+    # True: some of the architecture's sizes stand in the checkpoint's tensor shapes only; its
+    # config_from_dict takes them as a second argument (tensor name -> shape, or None without a checkpoint)
+    reads_shapes: bool = False
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_from_dict, build_spec) -> None:
-    _ARCHITECTURES[name] = Architecture(name, config_from_dict, build_spec)
+def register_architecture(name: str, config_from_dict, build_spec, reads_shapes: bool = False) -> None:
+    _ARCHITECTURES[name] = Architecture(name, config_from_dict, build_spec, reads_shapes)
 
 
 def get_architecture(name: str) -> Architecture:

@@ -57,7 +57,15 @@ def lib_path() -> str:
 _vp, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 
 _SIGNATURES = {
-    "atom_embedding": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "atom_embedding": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
+    "atom_xielu": [_vp, _vp, _i, _i64, _f, _f, _vp],
+    "atom_tanh": [_vp, _i, _i64, _vp],
+    "atom_pair_rmsnorm_add": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
+    "atom_token_shift_mix": [_vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "atom_wkv": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "atom_kv_write": [_vp, _i, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp, _vp, _i64, _vp, _vp],
+    "atom_attention_mixed": [_vp, _vp, _i64, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
+                             _vp, _i, _vp, _i, _vp, _vp, _f, _i, _vp],
     "atom_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp],
     "atom_rmsnorm": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
@@ -174,14 +182,14 @@ def _cuda(*tensors) -> None:
 # --------------------------------------------------------------------------- wrappers
 
 
-def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] widened to float32.  out [T,H] f32, table [V,H], ids [T] i32."""
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale widened to float32.  out [T,H] f32, table [V,H], ids [T] i32."""
     _cuda(out, table, ids)
     T, H = out.shape
     assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
     assert out.is_contiguous() and table.is_contiguous() and ids.numel() >= T
     _check(lib().atom_embedding(out.data_ptr(), table.data_ptr(), dtype_code(table.dtype),
-                                ids.data_ptr(), T, H, table.shape[0], _stream()), "embedding")
+                                ids.data_ptr(), T, H, table.shape[0], float(scale), _stream()), "embedding")
 
 
 def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: Optional[torch.Tensor],
@@ -207,6 +215,119 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float
     _check(lib().atom_rmsnorm(out.data_ptr(), x.data_ptr(), dtype_code(x.dtype), weight.data_ptr(),
                               dtype_code(weight.dtype), float(eps), x.numel() // H, H, _stream()),
            "rmsnorm")
+
+
+def xielu(out: torch.Tensor, x: torch.Tensor, ap: float, aq: float) -> None:
+    """out = xIELU(x) elementwise: ap z^2 + z/2 for z > 0, (1/2 + aq)(exp(z) - 1 - z) + z/2 otherwise."""
+    _cuda(out, x)
+    assert out.shape == x.shape and out.dtype == x.dtype and out.is_contiguous() and x.is_contiguous()
+    _check(lib().atom_xielu(out.data_ptr(), x.data_ptr(), dtype_code(x.dtype), x.numel(), float(ap), float(aq),
+                            _stream()), "xielu")
+
+
+def tanh_(x: torch.Tensor) -> None:
+    """x = tanh(x) in place."""
+    _cuda(x)
+    assert x.is_contiguous()
+    _check(lib().atom_tanh(x.data_ptr(), dtype_code(x.dtype), x.numel(), _stream()), "tanh")
+
+
+def pair_rmsnorm_add(residual: torch.Tensor, a: torch.Tensor, wa: Optional[torch.Tensor], b: Optional[torch.Tensor],
+                     wb: Optional[torch.Tensor], c: Optional[torch.Tensor], eps: float) -> None:
+    """residual += 0.5 * (rmsnorm(a; wa) + rmsnorm(b; wb)) (+ c) in 32-bit; with b None: += rmsnorm(a; wa) (+ c);
+    with wa None as well: += a (+ c)."""
+    _cuda(residual, a, wa, b, wb, c)
+    M, H = a.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape[0] >= M and residual.shape[1] == H
+    assert a.is_contiguous() and (wa is None or wa.numel() == H)
+    for t in (b, c):
+        assert t is None or (t.shape == a.shape and t.dtype == a.dtype and t.is_contiguous())
+    assert (b is None) == (wb is None) and (wb is None or (wa is not None and wb.numel() == H and wb.dtype == wa.dtype))
+    _check(lib().atom_pair_rmsnorm_add(residual.data_ptr(), a.data_ptr(), _ptr(wa), _ptr(b), _ptr(wb),
+                                       dtype_code(wa.dtype) if wa is not None else F32, _ptr(c), dtype_code(a.dtype),
+                                       float(eps), M, H, _stream()), "pair_rmsnorm_add")
+
+
+def token_shift_mix(out: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor,
+                    seq_of_token: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
+                    write_state: bool = True) -> None:
+    """out[m, t] = h[t] + (h[t-1] - h[t]) * mu[m] within each request; a request's first token of the step takes
+    h[t-1] from its row of ``state`` [slots, W], which then takes the h of the request's last token."""
+    _cuda(out, h, mu, state, seq_of_token, cu_q, state_slots)
+    T, W = h.shape
+    n = mu.shape[0]
+    assert out.shape == (n, T, W) and out.dtype == h.dtype == state.dtype and mu.shape == (n, W)
+    assert out.is_contiguous() and h.is_contiguous() and mu.is_contiguous() and state.is_contiguous()
+    assert state.shape[1] == W and seq_of_token.dtype == cu_q.dtype == state_slots.dtype == torch.int32
+    _check(lib().atom_token_shift_mix(out.data_ptr(), h.data_ptr(), dtype_code(h.dtype), mu.data_ptr(),
+                                      dtype_code(mu.dtype), state.data_ptr(), seq_of_token.data_ptr(),
+                                      cu_q.data_ptr(), state_slots.data_ptr(), T, W, n, int(write_state),
+                                      _stream()), "token_shift_mix")
+
+
+def wkv_supports(dk: int, dv: int) -> bool:
+    return 0 < dk <= 128 and 0 < dv <= 256
+
+
+def wkv(y: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor, gate: torch.Tensor,
+        w0: torch.Tensor, u: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+        state_slots: torch.Tensor, num_seqs: int, heads: int, dk: int, dv: int, eps: float,
+        write_state: bool = True) -> None:
+    """The decayed linear recurrence with bonus of csrc/wkv.cu over every request's tokens of the step, followed by
+    the per-head unit norm, the channel weights and silu(gate).  state: [slots, heads, dk, dv] float32."""
+    _cuda(y, r, k, v, d, gate, w0, u, norm_w, state, cu_q, state_slots)
+    T = r.shape[0]
+    for t_, n_ in ((r, dk), (k, dk), (d, dk), (v, dv), (gate, dv), (y, dv)):
+        assert t_.shape == (T, heads * n_) and t_.is_contiguous()
+    assert r.dtype == k.dtype == v.dtype == gate.dtype == y.dtype and d.dtype in (r.dtype, torch.float32)
+    assert w0.dtype == u.dtype == norm_w.dtype and w0.numel() == u.numel() == heads * dk and norm_w.numel() == heads * dv
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dk, dv)
+    _check(lib().atom_wkv(y.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), dtype_code(r.dtype), d.data_ptr(),
+                          dtype_code(d.dtype), gate.data_ptr(), w0.data_ptr(), u.data_ptr(), norm_w.data_ptr(),
+                          dtype_code(w0.dtype), state.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), num_seqs,
+                          heads, dk, dv, float(eps), int(write_state), _stream()), "wkv")
+
+
+def kv_write(qkv: torch.Tensor, k_off: int, v_off: int, nkv: int, dk: int, dv: int, vnorm: bool, eps: float,
+             positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+             k_pages: torch.Tensor, v_pages: torch.Tensor, status: torch.Tensor) -> None:
+    """Writes the step's keys (columns k_off...) and values (columns v_off...) of the packed projection to their
+    pages; vnorm: every value head is first divided by its root mean square."""
+    _cuda(qkv, positions, seq_of_token, block_table, k_pages, v_pages, status)
+    assert qkv.stride(1) == 1 and k_pages.dtype == v_pages.dtype == qkv.dtype
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, dk) and tuple(v_pages.shape[1:]) == (nkv, page_size, dv)
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dtype == torch.int32
+    assert block_table.dim() == 2 and block_table.is_contiguous() and k_pages.shape[0] == v_pages.shape[0]
+    _check(lib().atom_kv_write(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), k_off, v_off, qkv.shape[0], nkv,
+                               dk, dv, int(vnorm), float(eps), positions.data_ptr(), seq_of_token.data_ptr(),
+                               block_table.data_ptr(), block_table.shape[1], page_size, k_pages.data_ptr(),
+                               v_pages.data_ptr(), k_pages.shape[0], status.data_ptr(), _stream()), "kv_write")
+
+
+def attention_mixed(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, nh: int, nkv: int,
+                    dk: int, dv: int, scale: float, window: int = 0, rel: Optional[torch.Tensor] = None,
+                    half: int = 0, thresholds: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                    sink: Optional[torch.Tensor] = None, temp_coef: float = 0.0, temp_every: int = 0) -> None:
+    """Causal paged attention whose heads' scores are mixed before the softmax (csrc/attention_mixed.cu), with a
+    bias by distance, a sink per head and a query temperature, each optional.  q: [T, >= nh * dk] (row stride
+    taken from the tensor); out: [T, nh * dv]; rel [rows, nh], mix [nh, nh], sink [nh] float32; thresholds int32."""
+    _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token, rel, thresholds, mix, sink)
+    T = out.shape[0]
+    page_size = k_pages.shape[2]
+    assert out.is_contiguous() and out.shape[1] == nh * dv and q.stride(1) == 1 and out.dtype == q.dtype == k_pages.dtype
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, dk) and tuple(v_pages.shape[1:]) == (nkv, page_size, dv)
+    assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    n_thr = 0 if thresholds is None else thresholds.numel()
+    for t_ in (rel, mix, sink):
+        assert t_ is None or (t_.dtype == torch.float32 and t_.is_contiguous())
+    assert rel is None or (rel.shape[1] == nh and rel.shape[0] >= half + n_thr + (1 if n_thr else 0))
+    assert thresholds is None or thresholds.dtype == torch.int32
+    _check(lib().atom_attention_mixed(
+        out.data_ptr(), q.data_ptr(), q.stride(0), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(), seq_of_token.data_ptr(), T,
+        nh, nkv, dk, dv, float(scale), int(window), _ptr(rel), int(half), _ptr(thresholds), n_thr, _ptr(mix),
+        _ptr(sink), float(temp_coef), int(temp_every), _stream()), "attention_mixed")
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:

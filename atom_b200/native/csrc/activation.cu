@@ -1,4 +1,4 @@
-// SiLU-gated product of the feed-forward: out[t, i] = silu(gu[t, i]) * gu[t, I + i],
+// Activations of the feed-forwards.  SiLU-gated product: out[t, i] = silu(gu[t, i]) * gu[t, I + i],
 // computed in 32-bit (silu(x) = x / (1 + exp(-x))).
 #include "common.cuh"
 
@@ -50,7 +50,59 @@ __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const 
   }
 }
 
+// xIELU, an activation with two shape numbers (given here already passed through softplus, ap and aq):
+//   z > 0:  ap * z^2 + z / 2;      z <= 0:  (1/2 + aq) * (exp(z) - 1 - z) + z / 2,
+// computed in 32-bit.  expm1f keeps the small-|z| branch exact.
+template <typename T>
+__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t n, float ap, float aq) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride) {
+    const float z = to_float(x[idx]);
+    const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(0.5f + aq, expm1f(z) - z, 0.5f * z);
+    out[idx] = from_float<T>(y);
+  }
+}
+
+// tanh in place, in 32-bit (the hidden layer of a low-rank projection).
+template <typename T>
+__global__ void tanh_kernel(T* __restrict__ x, int64_t n) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride)
+    x[idx] = from_float<T>(tanhf(to_float(x[idx])));
+}
+
 }  // namespace atom
+
+ATOM_EXPORT int atom_tanh(void* x, int dtype, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return ATOM_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::tanh_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)x, n);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::tanh_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, n);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
+ATOM_EXPORT int atom_xielu(void* out, const void* x, int dtype, int64_t n, float ap, float aq, cudaStream_t stream) {
+  if (n <= 0) return ATOM_OK;
+  const int threads = 256;
+  int64_t blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::xielu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (float*)out, (const float*)x, n, ap, aq);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::xielu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, n, ap, aq);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
 
 ATOM_EXPORT int atom_silu_mul(void* out, const void* gu, int dtype, int T, int I,
                               cudaStream_t stream) {

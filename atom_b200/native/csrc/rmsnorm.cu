@@ -145,7 +145,59 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
   }
 }
 
+// Two branches that end in an RMSNorm of their own, averaged into the residual stream, with an optional
+// third addend:   residual[row] += 0.5 * (rmsnorm(a; wa) + rmsnorm(b; wb)) (+ c),   all in 32-bit.
+// With b null there is one branch and no halving: residual[row] += rmsnorm(a; wa) (+ c); with wa null as
+// well a is added as it is: residual[row] += a (+ c).
+template <typename TA>
+__global__ void pair_rmsnorm_add_kernel(float* __restrict__ residual, const TA* __restrict__ a,
+                                        const void* __restrict__ wa, const TA* __restrict__ b,
+                                        const void* __restrict__ wb, int w_dtype, const TA* __restrict__ c,
+                                        float eps, int H) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  __shared__ float scratch[32];
+  const int64_t r = blockIdx.x;
+  const TA* ar = a + r * H;
+  const TA* br = b ? b + r * H : nullptr;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float x = to_float(ar[i]);
+    sa = fmaf(x, x, sa);
+    if (br) {
+      const float y = to_float(br[i]);
+      sb = fmaf(y, y, sb);
+    }
+  }
+  sa = block_sum(sa, scratch);
+  sb = block_sum(sb, scratch);
+  const float ra = rsqrtf(sa / (float)H + eps), rb = rsqrtf(sb / (float)H + eps);
+  float* res = residual + r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = to_float(ar[i]);
+    if (wa) v = v * ra * load_as_float(wa, w_dtype, i);
+    if (br) v = 0.5f * (v + to_float(br[i]) * rb * load_as_float(wb, w_dtype, i));
+    if (c) v += to_float(c[r * H + i]);
+    res[i] += v;
+  }
+}
+
 }  // namespace atom
+
+ATOM_EXPORT int atom_pair_rmsnorm_add(float* residual, const void* a, const void* wa, const void* b, const void* wb,
+                                      int w_dtype, const void* c, int act_dtype, float eps, int n_rows, int H,
+                                      cudaStream_t stream) {
+  if (n_rows <= 0) return ATOM_OK;
+  if (H <= 0 || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
+  const int threads = atom::norm_threads(H);
+  if (act_dtype == ATOM_F32)
+    atom::launch_pdl(atom::pair_rmsnorm_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, residual, (const float*)a, wa, (const float*)b, wb, w_dtype, (const float*)c, eps, H);
+  else if (act_dtype == ATOM_BF16)
+    atom::launch_pdl(atom::pair_rmsnorm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, residual, (const __nv_bfloat16*)a, wa, (const __nv_bfloat16*)b, wb, w_dtype, (const __nv_bfloat16*)c, eps, H);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
 
 ATOM_EXPORT int atom_add_rmsnorm(void* out, int act_dtype, float* residual, const void* delta,
                                  const void* w, int w_dtype, float eps, const int* rows, int n_rows,

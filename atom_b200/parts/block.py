@@ -10,12 +10,16 @@ cache slot holds.
 sum; each sub-block's output is added to it inside the next norm's kernel:
    r += delta;  a = norm1(r);  m = mixer(a);  r += m;  b = norm2(r);  delta' = ffn(b).
 
+"parallel" has one norm whose output both the mixer and the feed-forward read, and adds both to the residual:
+   r += delta;  h = norm(r);  r += mixer(h) + ffn(h)        (a layer may have no feed-forward).
+
 Between parts that say they can, an output travels as a product still to run and normalised rows
 as ``ScaledRows`` (parts/linear.py), so that in a step of few rows the norms need no kernel of their
 own; a part that says nothing gets and gives plain tensors.
 """
 from __future__ import annotations
 
+from .. import native
 from .linear import resolve
 from .registry import register
 
@@ -48,3 +52,25 @@ class PreNormBlock:
         m = _forward(self.mixer, a, step, cache, writes_cache)
         b = _add_norm(self.ffn_norm, residual, m, "norm.ffn", self.ffn)
         return _forward(self.ffn, b, step)
+
+
+@register("arrangement", "parallel")
+class ParallelBlock:
+    slots = {"norm": "norm", "mixer": "mixer", "ffn": "ffn"}
+    optional = ("ffn",)
+    takes_pending = False
+
+    def __init__(self, norm, mixer, ffn=None):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+
+    def run(self, residual, delta, step, cache, writes_cache):
+        """The sum goes into the 32-bit residual here (a mixer that says ``adds_to_residual`` does it in
+        its own last kernel), so there is nothing left for the next norm to add: returns None."""
+        h = self.norm.add_norm(residual, delta, "norm.parallel")
+        f = self.ffn.forward(h, step) if self.ffn is not None else None
+        if getattr(self.mixer, "adds_to_residual", False):
+            self.mixer.forward(h, step, cache, writes_cache, add_to=(residual, f))
+        else:
+            m = self.mixer.forward(h, step, cache, writes_cache)
+            native.pair_rmsnorm_add(residual[: m.shape[0]], m, None, None, None, f, 0.0)
+        return None

@@ -1,6 +1,6 @@
 """Token embedding (atom/model_ops/embed_head.py:177) and output head (:249-252).
 
-The embedding writes the 32-bit residual stream; the head multiplies the normalised rows
+The embedding writes the 32-bit residual stream (times a constant ``scale`` where a model has one); the head multiplies the normalised rows
 whose logits are wanted by the output matrix and returns 32-bit logits.  A tied head uses
 the embedding's table (atom/models/qwen3.py:339-340)."""
 from __future__ import annotations
@@ -20,15 +20,15 @@ from .spec import ParamSpec
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
-        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0):
+        self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
 
     def params(self) -> Dict[str, ParamSpec]:
         return {"weight": ParamSpec((self.vocab_size, self.hidden_size))}
 
     def forward(self, token_ids: torch.Tensor, T: int) -> torch.Tensor:
         out = self.rt.workspace.get("residual", (T, self.hidden_size), torch.float32)
-        native.embedding(out, self.w_weight, token_ids)
+        native.embedding(out, self.w_weight, token_ids, self.scale)
         return out
 
 

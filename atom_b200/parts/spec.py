@@ -20,10 +20,12 @@ class ParamSpec:
            "vector": norm weight or bias; held in bfloat16 unless stored (or run) in 32-bit.
            "table":  integer table, held as int32.
     init   distribution of the random-weights mode: "normal" N(0, 0.02^2), "norm" U(0.8, 1.2),
-           "zeros".
+           "zeros", "half" U(0.25, 0.75), "eye" (identity plus N(0, 0.02^2), square matrices).
     rows   when the parameter is several checkpoint tensors stacked along one axis, their extents
            along it.
     stack_dim   that axis (0: rows under one another, as q/k/v; 1: side by side).
+    members_lack_axis   the stacked checkpoint tensors have no such axis of their own (each is one
+           slice: vectors [n] stacked into [m, n]); every extent in ``rows`` is then 1.
     """
 
     shape: Tuple[int, ...]
@@ -31,6 +33,7 @@ class ParamSpec:
     init: str = "normal"
     rows: Optional[Tuple[int, ...]] = None
     stack_dim: int = 0
+    members_lack_axis: bool = False
 
 
 @dataclass(frozen=True)
@@ -92,6 +95,9 @@ class ModelSpec:
     # is, element for element, the tensor ``other``; present and different is a loading error.
     duplicate_tensors: Tuple[Tuple[str, str], ...] = ()
     eos_token_ids: Tuple[int, ...] = ()
+    # Longest request the engine takes when its own max_model_len is not given; None: max_position
+    # (for models whose design names no longest sequence, max_position is the engine's own bound).
+    default_max_len: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -114,6 +120,10 @@ class CacheNeed:
                   pages.  Giving ``num_kv_heads`` and ``head_dim`` instead stands for the two
                   entries "k" and "v" of that shape each.
     kind "state": one array of fixed shape per request, held in a slot.
+    Either kind may also name ``states``: arrays of fixed shape per request (``CacheEntry`` with the
+    whole shape, in the compute type unless ``dtype`` says otherwise), held in the request's slot and
+    all zeros at the request's first token.  A mixer that keeps pages and a recurrent state side by
+    side declares kind "pages" with ``states``; ``merged`` puts two mixers' needs together.
     """
 
     kind: str
@@ -123,8 +133,12 @@ class CacheNeed:
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
     entries: Tuple[CacheEntry, ...] = ()
+    states: Tuple[CacheEntry, ...] = ()
 
     def __post_init__(self):
+        names = [e.name for e in self.states]
+        if len(set(names)) != len(names) or any(not e.shape for e in self.states):
+            raise ValueError(f"state arrays need distinct names and a shape: {self.states}")
         if self.kind == "pages" and not self.entries:
             if self.num_kv_heads <= 0 or self.head_dim <= 0:
                 raise ValueError("a 'pages' cache need names its entries, or kv heads and head size")
@@ -139,3 +153,30 @@ class CacheNeed:
         if self.kind == "pages":
             return ("pages", self.entries, self.window)
         return ("state", self.state_shape, self.state_dtype)
+
+    @property
+    def keeps_state(self) -> bool:
+        return self.kind == "state" or bool(self.states)
+
+    @staticmethod
+    def merged(needs: Mapping[str, Optional["CacheNeed"]]) -> Optional["CacheNeed"]:
+        """The one need of a mixer made of several (name -> need of each): the pages of the one member
+        that keeps pages (more than one is refused: they would have to share a block table and a
+        window) and every member's state arrays, named ``<member>.<array>``; a member of kind "state"
+        gives the array ``<member>.state``."""
+        pages = [(n, c) for n, c in needs.items() if c is not None and c.kind == "pages"]
+        if len(pages) > 1:
+            raise ValueError(f"more than one member keeps pages: {[n for n, _ in pages]}")
+        states = []
+        for n, c in needs.items():
+            if c is None:
+                continue
+            if c.kind == "state" and c.state_shape:
+                states.append(CacheEntry(f"{n}.state", tuple(c.state_shape), c.state_dtype))
+            states += [CacheEntry(f"{n}.{e.name}", e.shape, e.dtype) for e in c.states]
+        if pages:
+            c = pages[0][1]
+            return CacheNeed("pages", window=c.window, entries=c.entries, states=tuple(states))
+        if states:
+            return CacheNeed("state", states=tuple(states))
+        return None

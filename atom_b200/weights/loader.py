@@ -59,9 +59,12 @@ def expected_tensors(model: Model) -> Dict[str, Tuple[str, str, int, Tuple[int, 
             rows = ps.rows if ps.rows is not None else (ps.shape[d],)
             if len(rows) != len(srcs) or sum(rows) != ps.shape[d]:
                 raise ValueError(f"{path}.{name}: {len(srcs)} source tensors for the split {rows} of axis {d}")
+            if ps.members_lack_axis and any(r != 1 for r in rows):
+                raise ValueError(f"{path}.{name}: members without the stacked axis are one slice each, not {rows}")
             off = 0
             for src, r in zip(srcs, rows):
-                out[src] = (f"{path}.{name}", name, off, tuple(ps.shape[:d]) + (r,) + tuple(ps.shape[d + 1:]), ps)
+                member = () if ps.members_lack_axis else (r,)      # the shape the file holds
+                out[src] = (f"{path}.{name}", name, off, tuple(ps.shape[:d]) + member + tuple(ps.shape[d + 1:]), ps)
                 off += r
     return out
 
@@ -140,7 +143,9 @@ def load_weights(model: Model, model_dir: str, compute: torch.dtype, device) -> 
         t = where[n].get_tensor(n)
         dst = out[key]
         d = ps.stack_dim
-        dst.narrow(d, off, shape[d]).copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t)
+        if ps.members_lack_axis:
+            t = t.unsqueeze(d)
+        dst.narrow(d, off, t.shape[d]).copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t)
     return out
 
 

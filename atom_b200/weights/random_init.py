@@ -1,7 +1,8 @@
 """Random weights: a model folder written from a configuration and a seed, and a fast
 on-device fill for benchmarks.
 
-Distributions: matrices and embeddings N(0, 0.02^2), norm weights U(0.8, 1.2), biases 0.
+Distributions: matrices and embeddings N(0, 0.02^2), norm weights U(0.8, 1.2), biases 0 (and the
+others that ``ParamSpec.init`` names).
 The folder writer draws every checkpoint tensor in the spec's order from one CPU generator
 in 32-bit and stores bfloat16, so the 32-bit and the bfloat16 engine read the same values.
 (The reference's dummy weights are unseeded xavier/ones, atom/model_loader/loader.py:178-227.)
@@ -27,6 +28,11 @@ def _draw(shape, init: str, gen: torch.Generator, device="cpu") -> torch.Tensor:
         return torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * _STD
     if init == "norm":
         return torch.rand(shape, generator=gen, dtype=torch.float32, device=device) * (_NORM_HI - _NORM_LO) + _NORM_LO
+    if init == "half":
+        return torch.rand(shape, generator=gen, dtype=torch.float32, device=device) * 0.5 + 0.25
+    if init == "eye":
+        return torch.eye(shape[0], shape[1], dtype=torch.float32, device=device) + \
+            torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * _STD
     if init == "zeros":
         return torch.zeros(shape, dtype=torch.float32, device=device)
     raise ValueError(f"unknown init '{init}'")
