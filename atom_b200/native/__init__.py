@@ -65,7 +65,8 @@ _SIGNATURES = {
     "atom_wkv": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "atom_kv_write": [_vp, _i, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp, _vp, _i64, _vp, _vp],
     "atom_attention_mixed": [_vp, _vp, _i64, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-                             _vp, _i, _vp, _i, _vp, _vp, _f, _i, _vp],
+                             _vp, _i, _vp, _i, _vp, _vp, _f, _i, _i, _vp, _vp],
+    "atom_attention_mixed_merge": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "atom_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp],
     "atom_rmsnorm": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
@@ -121,6 +122,8 @@ def set_option(name: str, value: int) -> None:
         raise NativeError(f"option {name!r} was refused")
     for l in _flash_libs.values():
         l.atom_flash_set_option(key, int(value))
+    for l in _mixtc_libs.values():
+        l.atom_mixtc_set_option(key, int(value))
 
 
 def reset_options() -> None:
@@ -308,10 +311,13 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v
                     block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, nh: int, nkv: int,
                     dk: int, dv: int, scale: float, window: int = 0, rel: Optional[torch.Tensor] = None,
                     half: int = 0, thresholds: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
-                    sink: Optional[torch.Tensor] = None, temp_coef: float = 0.0, temp_every: int = 0) -> None:
+                    sink: Optional[torch.Tensor] = None, temp_coef: float = 0.0, temp_every: int = 0,
+                    nsplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
     """Causal paged attention whose heads' scores are mixed before the softmax (csrc/attention_mixed.cu), with a
     bias by distance, a sink per head and a query temperature, each optional.  q: [T, >= nh * dk] (row stride
-    taken from the tensor); out: [T, nh * dv]; rel [rows, nh], mix [nh, nh], sink [nh] float32; thresholds int32."""
+    taken from the tensor); out: [T, nh * dv]; rel [rows, nh], mix [nh, nh], sink [nh] float32; thresholds int32.
+    nsplit > 1: every token's keys are shared out among nsplit blocks (steps of few tokens and long contexts);
+    scratch: float32, at least ``attention_mixed_scratch_elems`` elements."""
     _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token, rel, thresholds, mix, sink)
     T = out.shape[0]
     page_size = k_pages.shape[2]
@@ -323,11 +329,111 @@ def attention_mixed(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v
         assert t_ is None or (t_.dtype == torch.float32 and t_.is_contiguous())
     assert rel is None or (rel.shape[1] == nh and rel.shape[0] >= half + n_thr + (1 if n_thr else 0))
     assert thresholds is None or thresholds.dtype == torch.int32
+    assert nsplit == 1 or (scratch is not None and scratch.dtype == torch.float32 and scratch.is_cuda
+                           and scratch.numel() >= attention_mixed_scratch_elems(T, nh, dv, nsplit))
     _check(lib().atom_attention_mixed(
         out.data_ptr(), q.data_ptr(), q.stride(0), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(), seq_of_token.data_ptr(), T,
         nh, nkv, dk, dv, float(scale), int(window), _ptr(rel), int(half), _ptr(thresholds), n_thr, _ptr(mix),
-        _ptr(sink), float(temp_coef), int(temp_every), _stream()), "attention_mixed")
+        _ptr(sink), float(temp_coef), int(temp_every), int(nsplit), _ptr(scratch) if nsplit > 1 else None, _stream()),
+        "attention_mixed")
+    if nsplit > 1:
+        add_launches(1)      # (the kernel that puts the shares together)
+
+
+SM_COUNT = 148      # B200
+
+
+def attention_mixed_scratch_elems(T: int, nh: int, dv: int, nsplit: int) -> int:
+    return T * nsplit * nh * (dv + 2)
+
+
+def attention_mixed_splits(units: int, max_ctx_len: int, per_sm: int = 2) -> int:
+    """Into how many shares the attention with mixed heads cuts the keys of every unit of work (a token for the
+    plain kernel, a tile of 16 tokens for the tensor-core kernel): ``per_sm`` CTAs per SM fill the device; below
+    that the keys are shared out, in shares of at least 256."""
+    if units >= per_sm * SM_COUNT:
+        return 1
+    return max(1, min(per_sm * SM_COUNT // max(units, 1), -(-max_ctx_len // 256), 64))
+
+
+# ---- the same attention on the tensor cores (csrc/attention_mixed_tc.cu), compiled per (heads, kv heads, key size,
+# value size) on first use
+_mixtc_libs = {}
+_MIXTC_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _f, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _i, _i,
+              _vp, _vp]
+MIXED_TC = True      # False: the plain kernel also where the tensor-core kernel takes the sizes (measurements, tests)
+
+
+def attention_mixed_tc_supports(nh: int, nkv: int, dk: int, dv: int, n_thr: int, mixing: bool, dtype: torch.dtype) -> bool:
+    """bfloat16; key and value sizes in steps of 16; at most 16 heads whose output tiles (16 rows x heads x value
+    size, 32-bit) fit the registers of a CTA's 16 warps; everything in 227 KB of shared memory."""
+    if dtype != torch.bfloat16 or dk % 16 or dv % 16 or nh % nkv or not 1 <= nh <= 16 or n_thr > 256:
+        return False
+    group = nh // nkv
+    if nkv * (-(-(group * (dv // 16)) // 16)) * 8 > 64:
+        return False
+    smem = 2 * (nh * 16 * (dk + 8) + 64 * (max(dk, dv) + 8)) + 4 * nh * 16 * 72 + 4 * nh * nh \
+        + 4 * (3 * nh * 16 + 16) + 4 * (64 + 256) + 256
+    return smem <= 226 * 1024
+
+
+def mixtc_lib(nh: int, nkv: int, dk: int, dv: int):
+    key = (nh, nkv, dk, dv)
+    l = _mixtc_libs.get(key)
+    if l is None:
+        with _lock:
+            l = _mixtc_libs.get(key)
+            if l is None:
+                path = build_variant("attention_mixed_tc.cu", {"ATOM_MH_NH": nh, "ATOM_MH_NKV": nkv, "ATOM_MH_DK": dk,
+                                                               "ATOM_MH_DV": dv})
+                l = ctypes.CDLL(path)
+                l.atom_attention_mixed_tc.argtypes = _MIXTC_SIG
+                l.atom_attention_mixed_tc.restype = ctypes.c_int
+                l.atom_mixtc_set_option.argtypes = [_i, _i]
+                l.atom_mixtc_set_option.restype = ctypes.c_int
+                got = [ctypes.c_int() for _ in range(4)]
+                l.atom_mixtc_sizes(*[ctypes.byref(g) for g in got])
+                if tuple(g.value for g in got) != key:
+                    raise NativeBuildError(f"{path} was built for other sizes")
+                for k, v in _option_values.items():
+                    l.atom_mixtc_set_option(k, v)
+                _mixtc_libs[key] = l
+    return l
+
+
+def attention_mixed_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                       block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                       cu_q: torch.Tensor, num_seqs: int, nh: int, nkv: int, dk: int, dv: int, scale: float,
+                       window: int = 0, rel: Optional[torch.Tensor] = None, half: int = 0,
+                       thresholds: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                       sink: Optional[torch.Tensor] = None, temp_coef: float = 0.0, temp_every: int = 0,
+                       nsplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """``attention_mixed`` on the tensor cores: tiles of 16 consecutive tokens of a request (cu_q: [num_seqs + 1]
+    first token row of every request).  Sizes as ``attention_mixed_tc_supports`` says."""
+    _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token, cu_q, rel, thresholds, mix, sink)
+    T = out.shape[0]
+    page_size = k_pages.shape[2]
+    assert out.is_contiguous() and out.shape[1] == nh * dv and q.stride(1) == 1
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, dk) and tuple(v_pages.shape[1:]) == (nkv, page_size, dv)
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and cu_q.numel() >= num_seqs + 1
+    n_thr = 0 if thresholds is None else thresholds.numel()
+    for t_ in (rel, mix, sink):
+        assert t_ is None or (t_.dtype == torch.float32 and t_.is_contiguous())
+    assert rel is None or (rel.shape[1] == nh and rel.shape[0] >= half + n_thr + (1 if n_thr else 0))
+    assert nsplit == 1 or (scratch is not None and scratch.dtype == torch.float32
+                           and scratch.numel() >= attention_mixed_scratch_elems(T, nh, dv, nsplit))
+    tiles = -(-T // 16) + num_seqs
+    _check(mixtc_lib(nh, nkv, dk, dv).atom_attention_mixed_tc(
+        out.data_ptr(), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], page_size, positions.data_ptr(), cu_q.data_ptr(), num_seqs, tiles, float(scale),
+        int(window), _ptr(rel), int(half), _ptr(thresholds), n_thr, _ptr(mix), _ptr(sink), float(temp_coef),
+        int(temp_every), int(nsplit), _ptr(scratch) if nsplit > 1 else None, _stream()), "attention_mixed_tc")
+    if nsplit > 1:
+        _check(lib().atom_attention_mixed_merge(out.data_ptr(), dtype_code(out.dtype), scratch.data_ptr(),
+                                                seq_of_token.data_ptr(), T, nh, dv, nsplit, _stream()),
+               "attention_mixed_merge")
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:

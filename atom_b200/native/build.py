@@ -77,7 +77,7 @@ def build_dir() -> str:
 
 # Sources that are compiled per variant (one library per value of their -D parameters), on
 # first use by a model that needs that variant; everything else goes into the core library.
-VARIANT_SOURCES = {"attention_flash.cu"}
+VARIANT_SOURCES = {"attention_flash.cu", "attention_mixed_tc.cu"}
 
 
 def sources() -> List[str]:
@@ -223,11 +223,19 @@ def _prune(bdir: str, srcs: Sequence[str], tag: str, keep: set) -> None:
 PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 128, 256)
 
 
+# Sizes of the attention with mixed heads that the build check compiles ahead of use.
+PREBUILT_MIXED_HEADS = (
+    {"ATOM_MH_NH": 16, "ATOM_MH_NKV": 4, "ATOM_MH_DK": 128, "ATOM_MH_DV": 128},
+    {"ATOM_MH_NH": 4, "ATOM_MH_NKV": 2, "ATOM_MH_DK": 16, "ATOM_MH_DV": 32},
+)
+
+
 def build_all(verbose: bool = True) -> str:
     """Compiles the core library and the usual variants (the build check); returns the core's path."""
     core = build(verbose=verbose)
     with concurrent.futures.ThreadPoolExecutor(max(1, min(len(PREBUILT_HEAD_DIMS), os.cpu_count() or 1))) as ex:
         list(ex.map(lambda hd: build_variant("attention_flash.cu", {"ATOM_HD": hd}, verbose), PREBUILT_HEAD_DIMS))
+        list(ex.map(lambda d: build_variant("attention_mixed_tc.cu", d, verbose), PREBUILT_MIXED_HEADS))
     return core
 
 

@@ -11,7 +11,9 @@
 //
 // This is the plain kernel for any sizes: one block per query token takes all heads (the mixing needs
 // all heads' scores of a key at once) and walks the token's keys in chunks with a running maximum and
-// sum per head, which start at the sink's value and at one.
+// sum per head, which start at the sink's value and at one.  With few tokens in the step (decoding) the keys
+// of a token are shared out among `nsplit` blocks, each of which leaves its maximum, sum and unnormalised
+// output per head in a scratch array; a second kernel puts them together.
 #include "common.cuh"
 
 namespace atom {
@@ -83,7 +85,8 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
                        int page_size, const int* __restrict__ positions, const int* __restrict__ seq_of_token, int nh,
                        int nkv, int dk, int dv, float scale, int window, const float* __restrict__ rel, int half,
                        const int* __restrict__ thr, int n_thr, const float* __restrict__ mix,
-                       const float* __restrict__ sink, float temp_coef, int temp_every) {
+                       const float* __restrict__ sink, float temp_coef, int temp_every, int nsplit,
+                       float* __restrict__ part) {
   atom::pdl_trigger();
   atom::pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -112,9 +115,10 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
   if (mix)
     for (int i = threadIdx.x; i < nh * nh; i += kMixThreads) mix_s[i] = mix[i];
   for (int i = threadIdx.x; i < n_thr; i += kMixThreads) thr_s[i] = thr[i];
-  for (int h = threadIdx.x; h < nh; h += kMixThreads) {
-    m_s[h] = sink ? sink[h] : -INFINITY;
-    l_s[h] = sink ? 1.f : 0.f;
+  const int split = blockIdx.y;
+  for (int h = threadIdx.x; h < nh; h += kMixThreads) {      // the sink counts once: in the first share
+    m_s[h] = (sink && split == 0) ? sink[h] : -INFINITY;
+    l_s[h] = (sink && split == 0) ? 1.f : 0.f;
   }
   float acc[kMixMaxAcc];
 #pragma unroll
@@ -122,10 +126,16 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
   const int n_out = nh * dv;
   int lo = 0;
   if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
+  int hi = p + 1;
+  if (nsplit > 1) {      // this block's share of the keys: whole chunks, the first shares full
+    const int per = ((p + 1 - lo + nsplit - 1) / nsplit + kMixChunk - 1) / kMixChunk * kMixChunk;
+    lo += split * per;
+    hi = min(hi, lo + per);
+  }
   __syncthreads();
 
-  for (int c0 = lo; c0 <= p; c0 += kMixChunk) {
-    const int n = min(kMixChunk, p + 1 - c0);
+  for (int c0 = lo; c0 < hi; c0 += kMixChunk) {
+    const int n = min(kMixChunk, hi - c0);
     for (int jj = threadIdx.x; jj < n; jj += kMixThreads) {
       const int j = c0 + jj;
       page_s[jj] = bt[j / page_size] * page_size + (j % page_size);     // (page, place) folded; kv head added below
@@ -200,6 +210,19 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
     }
     __syncthreads();
   }
+  if (nsplit > 1) {
+    float* pt = part + ((int64_t)t * nsplit + split) * (n_out + 2 * nh);
+    for (int h = threadIdx.x; h < nh; h += kMixThreads) {
+      pt[h] = m_s[h];
+      pt[nh + h] = l_s[h];
+    }
+#pragma unroll
+    for (int a = 0; a < kMixMaxAcc; ++a) {
+      const int idx = threadIdx.x + a * kMixThreads;
+      if (idx < n_out) pt[2 * nh + idx] = acc[a];
+    }
+    return;
+  }
 #pragma unroll
   for (int a = 0; a < kMixMaxAcc; ++a) {
     const int idx = threadIdx.x + a * kMixThreads;
@@ -207,6 +230,33 @@ attention_mixed_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_s
       const int h = idx / dv;
       out[(int64_t)t * n_out + idx] = from_float<T>(acc[a] / l_s[h]);
     }
+  }
+}
+
+// Puts the shares of a token's keys together: per head the largest maximum M, the sums and outputs
+// rescaled by exp(m - M).  A share without keys has m = -inf and weighs nothing; the first share is
+// never empty.
+template <typename T>
+__global__ void attention_mixed_merge_kernel(T* __restrict__ out, const float* __restrict__ part,
+                                             const int* __restrict__ seq_of_token, int nh, int dv, int nsplit) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int t = blockIdx.x;
+  if (seq_of_token[t] < 0) return;
+  const int n_out = nh * dv, stride = n_out + 2 * nh;
+  const float* pt = part + (int64_t)t * nsplit * stride;
+  for (int idx = threadIdx.x; idx < n_out; idx += blockDim.x) {
+    const int h = idx / dv;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pt[(int64_t)s * stride + h]);
+    float L = 0.f, o = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m = pt[(int64_t)s * stride + h];
+      const float w = (m == -INFINITY) ? 0.f : expf(m - M);
+      L = fmaf(pt[(int64_t)s * stride + nh + h], w, L);
+      o = fmaf(pt[(int64_t)s * stride + 2 * nh + idx], w, o);
+    }
+    out[(int64_t)t * n_out + idx] = from_float<T>(o / L);
   }
 }
 
@@ -233,16 +283,34 @@ ATOM_EXPORT int atom_kv_write(const void* qkv, int dtype, int64_t ld, int k_off,
   return atom::check_launch();
 }
 
+// Puts together the shares that another kernel (attention_mixed_tc.cu) left in `part`.
+ATOM_EXPORT int atom_attention_mixed_merge(void* out, int dtype, const float* part, const int* seq_of_token, int T,
+                                           int nh, int dv, int nsplit, cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (nsplit < 1 || part == nullptr) return ATOM_ERR_ARG;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::attention_mixed_merge_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)out, part,
+                     seq_of_token, nh, dv, nsplit);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::attention_mixed_merge_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream,
+                     (__nv_bfloat16*)out, part, seq_of_token, nh, dv, nsplit);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
 // out: [T, nh * dv]; q: row t at q + t * q_stride, heads packed [nh, dk]; k_pages [pages, nkv, page, dk];
 // v_pages [pages, nkv, page, dv].  rel: [half + n_thr + 1, nh] float32 or null; thr: n_thr ascending distances;
 // mix: [nh, nh] float32 or null; sink: [nh] float32 or null; temp_every <= 0: no query temperature.
+// nsplit > 1: every token's keys are shared out among nsplit blocks; part: T * nsplit * nh * (dv + 2) floats.
 ATOM_EXPORT int atom_attention_mixed(void* out, const void* q, int64_t q_stride, int dtype, const void* k_pages,
                                      const void* v_pages, const int* block_table, int max_pages, int page_size,
                                      const int* positions, const int* seq_of_token, int T, int nh, int nkv, int dk,
                                      int dv, float scale, int window, const float* rel, int half, const int* thr,
                                      int n_thr, const float* mix, const float* sink, float temp_coef, int temp_every,
-                                     cudaStream_t stream) {
+                                     int nsplit, float* part, cudaStream_t stream) {
   if (T <= 0) return ATOM_OK;
+  if (nsplit < 1 || nsplit > 65535 || (nsplit > 1 && part == nullptr)) return ATOM_ERR_ARG;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || dk <= 0 || dv <= 0 || page_size <= 0 ||
       nh * dv > atom::kMixMaxAcc * atom::kMixThreads)
     return ATOM_ERR_ARG;
@@ -255,10 +323,13 @@ ATOM_EXPORT int atom_attention_mixed(void* out, const void* q, int64_t q_stride,
     if (smem > 48 * 1024)                                                                                          \
       cudaFuncSetAttribute(atom::attention_mixed_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                            (int)smem);                                                                             \
-    atom::launch_pdl(atom::attention_mixed_kernel<TT>, dim3(T), dim3(atom::kMixThreads), smem, stream, (TT*)out,   \
-                     (const TT*)q, q_stride, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages,       \
-                     page_size, positions, seq_of_token, nh, nkv, dk, dv, scale, window, rel, half, thr, n_thr,    \
-                     mix, sink, temp_coef, temp_every);                                                            \
+    atom::launch_pdl(atom::attention_mixed_kernel<TT>, dim3(T, nsplit), dim3(atom::kMixThreads), smem, stream,    \
+                     (TT*)out, (const TT*)q, q_stride, (const TT*)k_pages, (const TT*)v_pages, block_table,       \
+                     max_pages, page_size, positions, seq_of_token, nh, nkv, dk, dv, scale, window, rel, half,    \
+                     thr, n_thr, mix, sink, temp_coef, temp_every, nsplit, part);                                  \
+    if (nsplit > 1)                                                                                                \
+      atom::launch_pdl(atom::attention_mixed_merge_kernel<TT>, dim3(T), dim3(256), 0, stream, (TT*)out,            \
+                       (const float*)part, seq_of_token, nh, dv, nsplit);                                          \
   } while (0)
   if (dtype == ATOM_F32)
     ATOM_MIX_LAUNCH(float);

@@ -6,19 +6,22 @@
 // the request's state row between steps, and all arithmetic of the recurrence is 32-bit; r, k, v, d and
 // the gate come from matrix products in the activation type.
 //
-// One block per (request, head); thread j owns column j of S in registers (the columns do not depend on
-// one another), so a step costs dk multiply-adds per thread and token.  Tokens are staged through shared
-// memory in chunks: r, k and the decay of a chunk are converted (and the two exponentials taken) once,
-// by all threads, and read as broadcasts in the loop.  The order of the sums does not depend on how a
-// request's tokens are cut into steps or chunks.
+// One block per (request, head); a state column j (the columns do not depend on one another) belongs to
+// kWkvSplit neighbouring lanes, each of which keeps a quarter of the column's key channels in registers, so
+// a token costs dk / 4 multiply-adds per thread and two shuffles, and the token-to-token chain is short.
+// The bonus needs no pass over the state: sum_i r[i] u[i] k[i] v[j] = v[j] * b with one number b per token,
+// which is formed while the chunk is staged.  Tokens go through shared memory in chunks: r, k and the decay
+// of a chunk are converted (and the two exponentials taken) once, by all threads.  The order of the sums
+// does not depend on how a request's tokens are cut into steps or chunks.
 #include "common.cuh"
 
 namespace atom {
 
 constexpr int kWkvChunk = 16;
+constexpr int kWkvSplit = 4;      // lanes to a state column
 
 template <typename T, int DKP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
            const void* __restrict__ d, int d_dtype, const T* __restrict__ gate, const void* __restrict__ w0,
            const void* __restrict__ u, const void* __restrict__ norm_w, int vec_dtype, float* __restrict__ state,
@@ -26,6 +29,7 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
            float eps, int write_state) {
   atom::pdl_trigger();
   atom::pdl_wait();
+  constexpr int DKQ = DKP / kWkvSplit;        // channels per lane (a multiple of 4)
   extern __shared__ __align__(16) float smem[];
   float* r_s = smem;                          // [chunk][DKP]
   float* k_s = r_s + kWkvChunk * DKP;         // [chunk][DKP]
@@ -35,11 +39,14 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
   float* v_s = w0_s + DKP;                    // [chunk][dv]
   float* o_s = v_s + kWkvChunk * dv;          // [chunk][dv]
   __shared__ float rstd_s[kWkvChunk];
+  __shared__ float b_s[kWkvChunk];
 
   const int s = blockIdx.x, hd = blockIdx.y;
   const int t0 = cu_q[s], t1 = cu_q[s + 1];
   if (t1 <= t0) return;                       // a request without tokens in this step (padding)
-  const int j = threadIdx.x;
+  const int j = threadIdx.x / kWkvSplit, part = threadIdx.x % kWkvSplit;
+  const int i0 = part * DKQ;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int64_t ldk = (int64_t)heads * dk, ldv = (int64_t)heads * dv;
   float* S_g = state + (((int64_t)state_slots[s] * heads + hd) * dk) * dv;
 
@@ -47,9 +54,9 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
     u_s[i] = i < dk ? load_as_float(u, vec_dtype, (int64_t)hd * dk + i) : 0.f;
     w0_s[i] = i < dk ? load_as_float(w0, vec_dtype, (int64_t)hd * dk + i) : 0.f;
   }
-  float S[DKP];
+  float S[DKQ];
 #pragma unroll
-  for (int i = 0; i < DKP; ++i) S[i] = (i < dk && j < dv) ? S_g[(int64_t)i * dv + j] : 0.f;
+  for (int i = 0; i < DKQ; ++i) S[i] = (i0 + i < dk && j < dv) ? S_g[(int64_t)(i0 + i) * dv + j] : 0.f;
   __syncthreads();
 
   for (int c0 = t0; c0 < t1; c0 += kWkvChunk) {
@@ -72,25 +79,42 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
       v_s[e] = to_float(v[(int64_t)(c0 + c) * ldv + (int64_t)hd * dv + jj]);
     }
     __syncthreads();
+    // the bonus' number of every token: a warp per token, lanes stride over the channels
+    for (int c = warp; c < n; c += nwarps) {
+      float b = 0.f;
+      for (int i = lane; i < DKP; i += 32) b = fmaf(r_s[c * DKP + i] * u_s[i], k_s[c * DKP + i], b);
+      b = warp_sum(b);
+      if (lane == 0) b_s[c] = b;
+    }
+    __syncthreads();
     if (j < dv) {
+      const unsigned group_mask = 0xFu << (lane & ~3);
       for (int c = 0; c < n; ++c) {
         const float vj = v_s[c * dv + j];
-        const float* rr = r_s + c * DKP;
-        const float* kk = k_s + c * DKP;
-        const float* ww = w_s + c * DKP;
-        float acc = 0.f;
+        const float4* rr = reinterpret_cast<const float4*>(r_s + c * DKP + i0);
+        const float4* kk = reinterpret_cast<const float4*>(k_s + c * DKP + i0);
+        const float4* ww = reinterpret_cast<const float4*>(w_s + c * DKP + i0);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DKP; ++i) {
-          const float kv = kk[i] * vj;
-          acc = fmaf(rr[i], fmaf(u_s[i], kv, S[i]), acc);
-          S[i] = fmaf(ww[i], S[i], kv);
+        for (int m = 0; m < DKQ / 4; ++m) {
+          const float4 r4 = rr[m], k4 = kk[m], w4 = ww[m];
+          a0 = fmaf(r4.x, S[4 * m], a0);
+          a1 = fmaf(r4.y, S[4 * m + 1], a1);
+          a2 = fmaf(r4.z, S[4 * m + 2], a2);
+          a3 = fmaf(r4.w, S[4 * m + 3], a3);
+          S[4 * m] = fmaf(w4.x, S[4 * m], k4.x * vj);
+          S[4 * m + 1] = fmaf(w4.y, S[4 * m + 1], k4.y * vj);
+          S[4 * m + 2] = fmaf(w4.z, S[4 * m + 2], k4.z * vj);
+          S[4 * m + 3] = fmaf(w4.w, S[4 * m + 3], k4.w * vj);
         }
-        o_s[c * dv + j] = acc;
+        float acc = (a0 + a1) + (a2 + a3);
+        acc += __shfl_xor_sync(group_mask, acc, 1);      // (a column's lanes are neighbours in one warp)
+        acc += __shfl_xor_sync(group_mask, acc, 2);
+        if (part == 0) o_s[c * dv + j] = fmaf(b_s[c], vj, acc);
       }
     }
     __syncthreads();
     // each head's o over its root mean square: a warp per token
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int c = warp; c < n; c += nwarps) {
       float ss = 0.f;
       for (int jj = lane; jj < dv; jj += 32) ss = fmaf(o_s[c * dv + jj], o_s[c * dv + jj], ss);
@@ -109,8 +133,8 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
   }
   if (write_state && j < dv) {
 #pragma unroll
-    for (int i = 0; i < DKP; ++i)
-      if (i < dk) S_g[(int64_t)i * dv + j] = S[i];
+    for (int i = 0; i < DKQ; ++i)
+      if (i0 + i < dk) S_g[(int64_t)(i0 + i) * dv + j] = S[i];
   }
 }
 
@@ -119,7 +143,7 @@ static int launch_wkv(T* y, const T* r, const T* k, const T* v, const void* d, i
                       const void* w0, const void* u, const void* norm_w, int vec_dtype, float* state,
                       const int* cu_q, const int* state_slots, int S, int heads, int dk, int dv, float eps,
                       int write_state, cudaStream_t stream) {
-  const int threads = ((dv + 31) / 32) * 32;
+  const int threads = ((dv * kWkvSplit + 31) / 32) * 32;
   const int dkp = ((dk + 15) / 16) * 16;
   const size_t smem = sizeof(float) * ((size_t)3 * kWkvChunk * dkp + 2 * dkp + (size_t)2 * kWkvChunk * dv);
 #define ATOM_WKV_CASE(N)                                                                                         \

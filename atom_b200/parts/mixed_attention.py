@@ -30,8 +30,8 @@ def distance_thresholds(rows: int, max_distance: float) -> List[int]:
     """For a distance-bias table of ``rows`` rows: row(n) = n for n < rows/2, else
     min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(max_distance / (rows/2)) * (rows - rows/2))).
     Returns the distances at which rows rows/2 + 1, rows/2 + 2, ... begin (ascending), found by
-    evaluating the formula in 64-bit for every distance up to where the last row is reached, so that
-    the kernel compares integers and never takes a logarithm."""
+    evaluating the formula in 64-bit around the place where each row must begin, so that the kernel
+    compares integers and never takes a logarithm."""
     if rows < 2 or rows % 2:
         raise ValueError(f"a distance-bias table needs an even number of rows (>= 2), got {rows}")
     half = rows // 2
@@ -43,8 +43,12 @@ def distance_thresholds(rows: int, max_distance: float) -> List[int]:
     def row(n: int) -> int:
         return min(rows - 1, half + int(math.floor(math.log(n / half) / denom * steps)))
 
-    out, n = [], half
+    out = []
     for r in range(half + 1, rows):
+        # near half * (max_distance / half) ** ((r - half) / steps); the formula itself decides the exact place
+        n = max(half, int(half * (max_distance / half) ** ((r - half) / steps)) - 2)
+        while n > half and row(n - 1) >= r:
+            n -= 1
         while row(n) < r:
             n += 1
         out.append(n)
@@ -107,7 +111,34 @@ class MixedHeadAttention(Mixer):
                             step.positions, step.seq_of_token, bt, cache.page_size, cache.k_pages, cache.v_pages,
                             step.status)
         o = ws.get("mha.o", (T, nh * dv), dt)
-        native.attention_mixed(o, qkv, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token,
-                               nh, nkv, dk, dv, self.scale, self.window or 0, self._rel, self.bias_rows // 2,
-                               self._thr, self._talk, self._sink, self.temp_coef, self.temp_every)
+        tc, nsplit = self.launch_plan(step)
+        scratch = None
+        if nsplit > 1:
+            scratch = ws.get("mha.splits", (native.attention_mixed_scratch_elems(T, nh, dv, nsplit),), torch.float32)
+        if tc:
+            native.attention_mixed_tc(o, qkv, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token,
+                                      step.cu_q, step.num_seqs, nh, nkv, dk, dv, self.scale, self.window or 0, self._rel,
+                                      self.bias_rows // 2, self._thr, self._talk, self._sink, self.temp_coef,
+                                      self.temp_every, nsplit, scratch)
+        else:
+            native.attention_mixed(o, qkv, cache.k_pages, cache.v_pages, bt, step.positions, step.seq_of_token,
+                                   nh, nkv, dk, dv, self.scale, self.window or 0, self._rel, self.bias_rows // 2,
+                                   self._thr, self._talk, self._sink, self.temp_coef, self.temp_every, nsplit, scratch)
         return linear(o, self.w_o_weight, None, ws.get("mha.out", (T, self.hidden_size), dt))
+
+    def launch_plan(self, step):
+        """(whether the tensor-core kernel runs, into how many shares every token's or tile's keys are cut), from
+        the step's shape and its longest context (windowed layers never look further back than their window)."""
+        key = ("mixed_head_attention", self.nh, self.nkv, self.dk, self.dv, self.window or 0)
+        plan = step.plans.get(key)
+        if plan is None:
+            longest = min(step.max_ctx_len, self.window) if self.window else step.max_ctx_len
+            tc = native.MIXED_TC and native.attention_mixed_tc_supports(
+                self.nh, self.nkv, self.dk, self.dv, len(self._thr_host), self.head_mixing, self.rt.dtype)
+            if tc:      # CTAs are tiles of 16 tokens of one request
+                units = max(step.num_seqs, -(-step.num_tokens // 16))
+                plan = (True, native.attention_mixed_splits(units, longest, per_sm=1))
+            else:
+                plan = (False, native.attention_mixed_splits(step.num_tokens, longest))
+            step.plans[key] = plan
+        return plan

@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
+    python bench.py --designs [SIZES]     (another workload: see the end of this text)
 
 The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 heads, 8 kv heads,
 head size 128, feed-forward 12288, vocabulary 151936, untied output matrix) with seeded
@@ -23,6 +24,10 @@ The engine is set up as a user gets it: ``max_model_len`` is the model's max_pos
 
 Every weight matrix of the model (tens of GB) is read in every step, far more than the
 126 MB L2 holds, so consecutive timed steps do not find their inputs in L2.
+
+``--designs`` leaves all of the above aside and prints the JSON line of ``atom_b200.benchmarks.designs``:
+prefill and decode throughput of the Nurinex design beside Qwen3 dense at equal layer sizes
+(``--designs 2048x16,4096x32``: width x attention heads; ``--designs-kernels`` adds every kernel's time).
 """
 from __future__ import annotations
 
@@ -175,8 +180,14 @@ def main() -> int:
     ap.add_argument("--only-measured-graphs", action="store_true",
                     help="capture only the decode graphs of the measured batch sizes and none for small mixed steps "
                          "(a short start-up, for runs under a profiler)")
+    ap.add_argument("--designs", nargs="?", const="2048x16,4096x32", default=None, metavar="SIZES",
+                    help="instead of the default workload: Nurinex beside Qwen3 dense at these sizes (width x heads, ...)")
+    ap.add_argument("--designs-kernels", action="store_true", help="with --designs: list every kernel's device time")
     args = ap.parse_args()
 
+    if args.designs is not None:
+        from atom_b200.benchmarks import designs
+        return designs.main(["--sizes", args.designs] + (["--kernels"] if args.designs_kernels else []))
     if args.impl == "reference":
         print(json.dumps(reference_arm()))
         return 0

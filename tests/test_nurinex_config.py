@@ -115,7 +115,8 @@ def test_configurations_that_are_refused():
     assert config_from_dict(c, None).layers[0].left.bias_rows == 8
 
 
-@pytest.mark.parametrize("rows,reach", [(8, 50), (32, 128), (4, 1000), (16, 40.5), (12, 30), (2, 3), (64, 4096), (32, 256)])
+@pytest.mark.parametrize("rows,reach", [(8, 50), (32, 128), (4, 1000), (16, 40.5), (12, 30), (2, 3), (64, 4096), (32, 256),
+                                        (6, 3.5), (16, 8.25), (8, 72)])
 def test_bias_rows_by_thresholds_equal_the_formula(rows, reach):
     """The kernel finds a distance's row by counting the thresholds at or below it."""
     thr = distance_thresholds(rows, reach)
@@ -124,3 +125,10 @@ def test_bias_rows_by_thresholds_equal_the_formula(rows, reach):
     for n in range(0, int(reach * 3) + 50):
         row = n if n < half else half + sum(1 for t in thr if t <= n)
         assert row == plain.bias_row(n, rows, reach), (n, row)
+
+
+def test_thresholds_of_a_table_that_reaches_very_far():
+    thr = distance_thresholds(32, 1e9)            # (found around their places, not by walking there)
+    assert len(thr) == 15 and thr == sorted(thr)
+    for t in thr:
+        assert plain.bias_row(t, 32, 1e9) == plain.bias_row(t - 1, 32, 1e9) + 1

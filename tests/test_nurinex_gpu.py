@@ -47,7 +47,7 @@ class Paged:
         self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
 
 
-def _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts, eps=1e-5, value_norm=True):
+def _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts, eps=1e-5, value_norm=True, nsplit=0, kernel="plain"):
     """Feeds T tokens of one request in portions ``cuts`` through kv_write + attention_mixed; q [T,H,dk],
     k [T,G,dk], v [T,G,dv] float64.  Returns [T, H*dv] (float64, on the CPU)."""
     from atom_b200 import native
@@ -74,9 +74,16 @@ def _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts, eps=1e-5, val
         part = qkv[at:at + n]
         native.kv_write(part, H * dk, (H + G) * dk, G, dk, dv, value_norm, eps, pos, sot, cache.table, page,
                         cache.k_pages, cache.v_pages, cache.status)
-        native.attention_mixed(out[at:at + n], part, cache.k_pages, cache.v_pages, cache.table, pos, sot, H, G, dk, dv,
-                               c["scale"], 0, f32(rel), rows // 2, thr, f32(talk), f32(sink),
-                               c["q_temp"]["coef"], c["q_temp"]["every"])
+        args = (H, G, dk, dv, c["scale"], 0, f32(rel), rows // 2, thr, f32(talk), f32(sink), c["q_temp"]["coef"], c["q_temp"]["every"])
+        if kernel == "tc":
+            ns = nsplit or native.attention_mixed_splits(-(-n // 16), at + n, per_sm=1)        # (0: as the mixer chooses)
+            scratch = torch.empty(native.attention_mixed_scratch_elems(n, H, dv, ns), dtype=torch.float32, device=DEV) if ns > 1 else None
+            cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+            native.attention_mixed_tc(out[at:at + n], part, cache.k_pages, cache.v_pages, cache.table, pos, sot, cu, 1, *args, ns, scratch)
+        else:
+            ns = nsplit or native.attention_mixed_splits(n, at + n)
+            scratch = torch.empty(native.attention_mixed_scratch_elems(n, H, dv, ns), dtype=torch.float32, device=DEV) if ns > 1 else None
+            native.attention_mixed(out[at:at + n], part, cache.k_pages, cache.v_pages, cache.table, pos, sot, *args, ns, scratch)
         at += n
     assert at == T and int(cache.status.item()) == 0
     return out.double().cpu()
@@ -93,6 +100,14 @@ def _plain_attention(q, k, v, c, rel, talk, sink, eps=1e-5, value_norm=True):
         w = plain.sink_softmax(s, sink)
     vv = plain.unit_rms(v, eps) if value_norm else v
     return torch.einsum("hij,jhd->ihd", w, vv.repeat_interleave(H // G, dim=1)).reshape(T, -1)
+
+
+def _kernels(H, G, dk, dv, rows, mixing, dtype):
+    """The kernels that take these sizes: the plain one always, the tensor-core one where it does."""
+    from atom_b200 import native
+    n_thr = max(0, rows - rows // 2 - 1)
+    tc = native.attention_mixed_tc_supports(H, G, dk, dv, n_thr, mixing, _dt(dtype))
+    return ["plain", "tc"] if tc else ["plain"]
 
 
 def _rounded(t, dtype):
@@ -116,6 +131,9 @@ ATT_CASES = [
     (5, 5, 20, 12, 12, 30.0, 0.3, 5, 4),
     (8, 2, 128, 128, 32, 128.0, 0.5, 32, 32),
     (1, 1, 64, 64, 2, 3.0, 0.0, 7, 16),
+    (16, 4, 64, 64, 24, 300.0, 0.4, 16, 16),
+    (8, 8, 48, 80, 10, 64.0, 0.2, 3, 8),
+    (16, 4, 128, 128, 32, 128.0, 0.5, 64, 16),
 ]
 
 
@@ -131,9 +149,31 @@ def test_attention_with_every_extra(case, dtype):
     talk = (torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)).to(torch.bfloat16).double()
     sink = torch.randn(H, generator=g).to(torch.bfloat16).double()
     want = _plain_attention(q, k, v, c, rel, talk, sink)
-    for cuts in ([T], [1] * T, [37, 2, 2, 50, 1, 1, 3, 29, 25], [149, 1]):
-        got = _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts)
-        _close(got, want, dtype, f"cuts {cuts[:4]}")
+    for kernel in _kernels(H, G, dk, dv, rows, True, dtype):
+        for cuts in ([T], [1] * T, [37, 2, 2, 50, 1, 1, 3, 29, 25], [149, 1]):
+            got = _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts, kernel=kernel)
+            _close(got, want, dtype, f"{kernel}, cuts {cuts[:4]}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nsplit", [2, 3, 7, 64])
+def test_attention_with_keys_shared_out_among_blocks(nsplit, dtype):
+    """Shares of whole chunks of keys, some of them empty for the first tokens; the sink counts in the first only."""
+    H, G, dk, dv, rows, reach, coef, every, page = ATT_CASES[0]
+    T = 330
+    c = {"scale": 1.7 / dk ** 0.5, "bias_max": reach, "q_temp": {"coef": coef, "every": every}}
+    q, k, v = _qkv(T, H, G, dk, dv, dtype, seed=nsplit)
+    g = torch.Generator().manual_seed(7)
+    rel = torch.randn(rows, H, generator=g).to(torch.bfloat16).double()
+    talk = (torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)).to(torch.bfloat16).double()
+    sink = torch.randn(H, generator=g).to(torch.bfloat16).double()
+    want = _plain_attention(q, k, v, c, rel, talk, sink)
+    for kernel in _kernels(H, G, dk, dv, rows, True, dtype):
+        for cuts in ([T], [300] + [1] * 30):
+            got = _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts, nsplit=nsplit, kernel=kernel)
+            _close(got, want, dtype, f"{kernel}, {nsplit} shares")
+        got = _run_attention(q, k, v, c, None, None, None, dtype, page, [129, 1, 200], nsplit=nsplit, kernel=kernel)
+        _close(got, _plain_attention(q, k, v, c, None, None, None), dtype, f"{kernel}, {nsplit} shares, no extras")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -161,8 +201,9 @@ def test_attention_extras_are_options(leave_out, dtype):
     if cp["q_temp"]["every"] == 0:
         cp["q_temp"] = {"coef": 0.0, "every": 1}
     want = _plain_attention(q, k, v, cp, rel, talk, sink, value_norm=vn)
-    got = _run_attention(q, k, v, c, rel, talk, sink, dtype, page, [33, 1, 1, 35], value_norm=vn)
-    _close(got, want, dtype, leave_out)
+    for kernel in _kernels(H, G, dk, dv, 8 if rel is not None else 0, talk is not None, dtype):
+        got = _run_attention(q, k, v, c, rel, talk, sink, dtype, page, [33, 1, 1, 35], value_norm=vn, kernel=kernel)
+        _close(got, want, dtype, f"{leave_out}, {kernel}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -179,9 +220,9 @@ def test_one_far_key_among_hundreds_stands_out(needle, dtype):
     k[needle, 0, 5] = 6.0
     q[T - 1, :, 5] = 6.0
     want = _plain_attention(q, k, v, c, None, None, torch.zeros(H, dtype=F64))
-    for cuts in ([T], [T - 3, 1, 1, 1]):
-        got = _run_attention(q, k, v, c, None, None, torch.zeros(H, dtype=F64), dtype, page, cuts)
-        _close(got, want, dtype, f"needle {needle}")
+    for kernel, cuts in [(kn, cu) for kn in _kernels(H, G, dk, dv, 0, False, dtype) for cu in ([T], [T - 3, 1, 1, 1])]:
+        got = _run_attention(q, k, v, c, None, None, torch.zeros(H, dtype=F64), dtype, page, cuts, kernel=kernel)
+        _close(got, want, dtype, f"needle {needle}, {kernel}")
         unit = plain.unit_rms(v, 1e-5)[needle, 0]
         assert (got[T - 1, :dv] - unit).abs().max() < 0.05, "the far key's value did not come back"
 
@@ -204,25 +245,26 @@ def test_bias_row_edges_in_prompts_and_in_decoding(rows, reach, dtype):
         rel[row, 0] = 30.0
         rel[(row + 1) % rows, 1] = 30.0
         want = _plain_attention(q, k, v, c, rel, None, None)
-        for cuts in ([T], [T // 2] + [1] * (T - T // 2)):
-            got = _run_attention(q, k, v, c, rel, None, None, dtype, page, cuts)
-            _close(got, want, dtype, f"row {row}")
+        for kernel, cuts in [(kn, cu) for kn in _kernels(H, G, dk, dv, rows, False, dtype) for cu in ([T], [T // 2] + [1] * (T - T // 2))]:
+            got = _run_attention(q, k, v, c, rel, None, None, dtype, page, cuts, kernel=kernel)
+            _close(got, want, dtype, f"row {row}, {kernel}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sink_counts_once_and_has_no_value(dtype):
     """Zero scores: every key weighs 1 / (keys + exp(sink)); the first tokens of a sequence feel it most."""
-    H, G, dk, dv, page, T = 3, 3, 16, 8, 4, 40
+    H, G, dk, dv, page, T = 3, 3, 16, 16, 4, 40
     c = {"scale": 1.0, "bias_max": 10.0, "q_temp": {"coef": 0.0, "every": 1}}
     g = torch.Generator().manual_seed(1)
     v = _rounded(torch.randn(T, G, dv, generator=g), dtype)
     z = torch.zeros(T, H, dk, dtype=F64)
     sink = torch.tensor([-2.0, 0.0, 3.0], dtype=F64)
-    got = _run_attention(z, z[:, :G], v, c, None, None, sink, dtype, page, [5] + [1] * 35, value_norm=False)
-    for h in range(H):
-        for i in (0, 1, 2, 7, 39):
-            want = v[: i + 1, h].sum(0) / (i + 1 + math.exp(float(sink[h])))
-            _close(got[i, h * dv:(h + 1) * dv], want, dtype, f"head {h} token {i}", scale=1.0)
+    for kernel in _kernels(H, G, dk, dv, 0, False, dtype):
+        got = _run_attention(z, z[:, :G], v, c, None, None, sink, dtype, page, [5] + [1] * 35, value_norm=False, kernel=kernel)
+        for h in range(H):
+            for i in (0, 1, 2, 7, 39):
+                want = v[: i + 1, h].sum(0) / (i + 1 + math.exp(float(sink[h])))
+                _close(got[i, h * dv:(h + 1) * dv], want, dtype, f"head {h} token {i}, {kernel}", scale=1.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -241,8 +283,8 @@ def test_query_temperature_steps_at_whole_blocks(every, dtype):
     k[0, 0, 0], k[1, 0, 0] = a, -a
     k[2:, 0, 0] = -50.0                       # the other keys do not count
     v[0, 0, 0], v[1, 0, 1] = 1.0, 1.0
-    for cuts in ([T], [2] + [1] * (T - 2)):
-        got = _run_attention(q, k, v, c, None, None, None, dtype, page, cuts, value_norm=False)
+    for kernel, cuts in [(kn, cu) for kn in _kernels(H, G, dk, dv, 0, False, dtype) for cu in ([T], [2] + [1] * (T - 2))]:
+        got = _run_attention(q, k, v, c, None, None, None, dtype, page, cuts, value_norm=False, kernel=kernel)
         for p in range(1, T):
             t = plain.query_temperature(p, coef, every)
             assert abs(t - (1 + coef * math.log((p + 1) // every + 1))) < 1e-12
