@@ -269,7 +269,7 @@ def token_shift_mix(out: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state:
 
 
 def wkv_supports(dk: int, dv: int) -> bool:
-    return 0 < dk <= 128 and 0 < dv <= 256
+    return 0 < dk <= 128 and 0 < dv <= 128
 
 
 def wkv(y: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor, gate: torch.Tensor,
@@ -348,13 +348,14 @@ def attention_mixed_scratch_elems(T: int, nh: int, dv: int, nsplit: int) -> int:
     return T * nsplit * nh * (dv + 2)
 
 
-def attention_mixed_splits(units: int, max_ctx_len: int, per_sm: int = 2) -> int:
+def attention_mixed_splits(units: int, max_ctx_len: int, per_sm: int = 2, min_share: int = 256) -> int:
     """Into how many shares the attention with mixed heads cuts the keys of every unit of work (a token for the
-    plain kernel, a tile of 16 tokens for the tensor-core kernel): ``per_sm`` CTAs per SM fill the device; below
-    that the keys are shared out, in shares of at least 256."""
+    plain kernel, a tile of 16 tokens for the tensor-core kernel): ``per_sm`` CTAs per SM fill the device (and even
+    out the unequal lengths of a prompt's tiles); below that the keys are shared out, in shares of at least
+    ``min_share``."""
     if units >= per_sm * SM_COUNT:
         return 1
-    return max(1, min(per_sm * SM_COUNT // max(units, 1), -(-max_ctx_len // 256), 64))
+    return max(1, min(-(-per_sm * SM_COUNT // max(units, 1)), -(-max_ctx_len // min_share), 64))
 
 
 # ---- the same attention on the tensor cores (csrc/attention_mixed_tc.cu), compiled per (heads, kv heads, key size,
@@ -373,8 +374,8 @@ def attention_mixed_tc_supports(nh: int, nkv: int, dk: int, dv: int, n_thr: int,
     group = nh // nkv
     if nkv * (-(-(group * (dv // 16)) // 16)) * 8 > 64:
         return False
-    smem = 2 * (nh * 16 * (dk + 8) + 64 * (max(dk, dv) + 8)) + 4 * nh * 16 * 72 + 4 * nh * nh \
-        + 4 * (3 * nh * 16 + 16) + 4 * (64 + 256) + 256
+    smem = 2 * (nh * 16 * (dk + 8) + 2 * 64 * (max(dk, dv) + 8)) + 4 * nh * 16 * 72 + 4 * nh * nh \
+        + 4 * (3 * nh * 16 + 16) + 4 * (2 * 64 + 256) + 256
     return smem <= 226 * 1024
 
 

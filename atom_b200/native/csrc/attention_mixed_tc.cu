@@ -4,7 +4,7 @@
 //
 // A CTA of 16 warps takes a tile of 16 consecutive tokens of one request with ALL heads, because mixing the
 // heads needs every head's score of a (query, key) pair at once, and walks the keys in chunks of 64:
-//   1. per kv head: its 64 keys go to shared memory; S_h = Q_h K^T for the heads of its group on mma.sync
+//   1. per kv head: its 64 keys go to shared memory (cp.async, the next load under way while this one is used); S_h = Q_h K^T for the heads of its group on mma.sync
 //      (m16n8k16, 32-bit sums), times scale * temperature of the row, plus the distance bias, to shared
 //      memory in 32-bit;
 //   2. warp r owns row r: it takes the row's raw scores of all heads into registers, forms every head's
@@ -40,8 +40,8 @@ static_assert(NH % NKV == 0 && DK % 16 == 0 && DV % 16 == 0, "sizes");
 static_assert(NKV * TPG * 8 <= 64, "output tiles of a warp exceed its registers");
 
 constexpr size_t smem_bytes(bool mix) {
-  return sizeof(__nv_bfloat16) * ((size_t)NH * BM * LDQ + (size_t)BN * LDKV) + sizeof(float) * ((size_t)NH * BM * LDR) +
-         sizeof(float) * (mix ? NH * NH : 0) + sizeof(float) * (3 * NH * BM + BM) + sizeof(int) * (BN + MAX_THR) +
+  return sizeof(__nv_bfloat16) * ((size_t)NH * BM * LDQ + (size_t)2 * BN * LDKV) + sizeof(float) * ((size_t)NH * BM * LDR) +
+         sizeof(float) * (mix ? NH * NH : 0) + sizeof(float) * (3 * NH * BM + BM) + sizeof(int) * (2 * BN + MAX_THR) +
          sizeof(short) * 128;
 }
 
@@ -63,12 +63,52 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 16 bytes global -> shared without passing through registers; !valid: 16 zero bytes, nothing is read.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 __device__ __forceinline__ int distance_row(int n, int half, const int* thr, int n_thr) {
   if (n < half) return n;
   int b = 0;
   for (int k = 0; k < n_thr; ++k) b += (thr[k] <= n) ? 1 : 0;
   return half + b;
 }
+
+// Reduces N values per lane (N a power of two up to 16) over the warp with N - 1 + (5 - log2 N) shuffles instead of
+// 5 N: in every halving step a lane hands over the half of its values that its partner keeps.  Afterwards lane L
+// holds, in v[0], the warp's total of element (L >> (5 - log2 N)) & (N - 1).
+template <int N, bool IS_MAX>
+__device__ __forceinline__ float reduce_many(float (&v)[N], int lane) {
+  int off = 16;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = upper ? v[i] : v[i + n / 2];
+      const float keep = upper ? v[i + n / 2] : v[i];
+      const float got = __shfl_xor_sync(0xffffffffu, send, off);
+      v[i] = IS_MAX ? fmaxf(keep, got) : keep + got;
+    }
+    off >>= 1;
+  }
+  float t = v[0];
+  for (; off > 0; off >>= 1) {
+    const float got = __shfl_xor_sync(0xffffffffu, t, off);
+    t = IS_MAX ? fmaxf(t, got) : t + got;
+  }
+  return t;
+}
+
+constexpr int NHP = NH <= 1 ? 1 : (NH <= 2 ? 2 : (NH <= 4 ? 4 : (NH <= 8 ? 8 : 16)));      // heads, rounded up to a power of two
+constexpr int LOG_NHP = NHP == 1 ? 0 : (NHP == 2 ? 1 : (NHP == 4 ? 2 : (NHP == 8 ? 3 : 4)));
+static_assert(NH <= 16, "at most 16 heads");
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, int64_t q_stride,
@@ -82,15 +122,15 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
   atom::pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = (__nv_bfloat16*)smem_raw;                  // [NH][16][LDQ]
-  __nv_bfloat16* KVs = Qs + NH * BM * LDQ;                       // [64][LDKV]
-  float* raw = (float*)(KVs + BN * LDKV);                        // [NH][16][LDR]
+  __nv_bfloat16* KVs = Qs + NH * BM * LDQ;                       // [2][64][LDKV]: one kv head's keys or values, twice
+  float* raw = (float*)(KVs + 2 * BN * LDKV);                    // [NH][16][LDR]
   float* mix_s = raw + NH * BM * LDR;                            // [NH][NH] if mixing
   float* m_s = mix_s + (mix ? NH * NH : 0);                      // [NH][16]
   float* l_s = m_s + NH * BM;
   float* corr_s = l_s + NH * BM;
   float* qscale_s = corr_s + NH * BM;                            // [16]
-  int* off_s = (int*)(qscale_s + BM);                            // [64] row of a key in the pages, kv head 0
-  int* thr_s = off_s + BN;                                       // [MAX_THR]
+  int* off_s = (int*)(qscale_s + BM);                            // [2][64] row of a key in the pages, kv head 0
+  int* thr_s = off_s + 2 * BN;                                   // [MAX_THR]
   short* bkt_s = (short*)(thr_s + MAX_THR);                      // [128] bias row by (row - column + 63)
   __shared__ int tile_s[3];
 
@@ -157,16 +197,51 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
   }
   __syncthreads();
 
-  for (int c0 = lo; c0 < hi; c0 += BN) {
-    // ---- where the chunk's keys lie, and the bias row of every distance that occurs in the chunk
-    if (threadIdx.x < BN) {
-      const int j = c0 + threadIdx.x;
-      int off = -1;
-      if (j < hi) {
-        const int pg = bt[j / page_size];
-        off = pg * NKV * page_size + (j % page_size);
+  // The keys and values of a chunk come as 2 * NKV loads of one kv head's 64 rows each (K of every kv head, then
+  // V of every kv head), through two buffers: while the warps work on one load, the next is on its way.
+  int issued = 0, used = 0;
+  auto key_rows = [&](int c0_, int* offs) {      // threads 0..63: where chunk c0_'s keys lie
+    const int j = c0_ + threadIdx.x;
+    int off = -1;
+    if (j < hi) {
+      const int pg = bt[j / page_size];
+      off = pg * NKV * page_size + (j % page_size);
+    }
+    offs[threadIdx.x] = off;
+  };
+  auto issue = [&](int c0_, int i, const int* offs) {
+    __nv_bfloat16* dst = KVs + (issued & 1) * BN * LDKV;
+    if (c0_ < hi) {
+      if (i < NKV) {
+        for (int e = threadIdx.x; e < BN * (DK / 8); e += THREADS) {
+          const int seg = e % (DK / 8), key = e / (DK / 8);
+          const int off = offs[key];
+          cp_async16(dst + key * LDKV + seg * 8,
+                     off >= 0 ? k_pages + ((int64_t)off + (int64_t)i * page_size) * DK + seg * 8 : k_pages, off >= 0);
+        }
+      } else {
+        for (int e = threadIdx.x; e < BN * (DV / 8); e += THREADS) {
+          const int seg = e % (DV / 8), key = e / (DV / 8);
+          const int off = offs[key];
+          cp_async16(dst + key * LDKV + seg * 8,
+                     off >= 0 ? v_pages + ((int64_t)off + (int64_t)(i - NKV) * page_size) * DV + seg * 8 : v_pages, off >= 0);
+        }
       }
-      off_s[threadIdx.x] = off;
+    }
+    cp_async_commit();
+    ++issued;
+  };
+  if (threadIdx.x < BN) key_rows(lo, off_s);
+  __syncthreads();
+  issue(lo, 0, off_s);
+
+  int ci = 0;
+  for (int c0 = lo; c0 < hi; c0 += BN, ++ci) {
+    const int* cur = off_s + (ci & 1) * BN;
+    int* nxt = off_s + ((ci + 1) & 1) * BN;
+    // ---- where the next chunk's keys lie, and the bias row of every distance that occurs in this chunk
+    if (threadIdx.x < BN) {
+      key_rows(c0 + BN, nxt);
     } else if (rel && threadIdx.x >= 64 && threadIdx.x < 64 + BM + BN - 1) {
       const int dlt = threadIdx.x - 64;                           // row - column + 63
       const int n = (p0 - c0) + dlt - (BN - 1);
@@ -177,20 +252,17 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
     // ---- 1. raw scores of every head
 #pragma unroll 1
     for (int g = 0; g < NKV; ++g) {
-      for (int e = threadIdx.x; e < BN * (DK / 8); e += THREADS) {
-        const int seg = e % (DK / 8), key = e / (DK / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        const int off = off_s[key];
-        if (off >= 0) v = *reinterpret_cast<const uint4*>(k_pages + ((int64_t)off + (int64_t)g * page_size) * DK + seg * 8);
-        *reinterpret_cast<uint4*>(KVs + key * LDKV + seg * 8) = v;
-      }
+      issue(c0, g + 1, cur);                                      // the next kv head's keys, or the first one's values
+      cp_async_wait<1>();
       __syncthreads();
+      const __nv_bfloat16* Ks = KVs + (used & 1) * BN * LDKV;
+      ++used;
       for (int u = warp; u < QK_UNITS; u += WARPS) {
         const int hq = u / (BN / 16), kb = u % (BN / 16);
         const int h = g * GROUP + hq;
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         const __nv_bfloat16* qbase = Qs + (h * BM + (mat & 1) * 8 + r8) * LDQ + (mat >> 1) * 8;
-        const __nv_bfloat16* kbase = KVs + (kb * 16 + (mat >> 1) * 8 + r8) * LDKV + (mat & 1) * 8;
+        const __nv_bfloat16* kbase = Ks + (kb * 16 + (mat >> 1) * 8 + r8) * LDKV + (mat & 1) * 8;
 #pragma unroll
         for (int ks = 0; ks < DK / 16; ++ks) {
           uint32_t a[4], b[4];
@@ -215,58 +287,85 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
 
     // ---- 2. mixing, mask, running softmax: warp r has row r
     {
+      constexpr int OWNER_SHIFT = 5 - LOG_NHP;                    // lane L answers for head (L >> OWNER_SHIFT) & (NHP - 1)
       const int r = warp;
       const int pr = p0 + r;
-      float x0[NH], x1[NH];
-#pragma unroll
-      for (int g = 0; g < NH; ++g) {
-        x0[g] = raw[(g * BM + r) * LDR + lane];
-        x1[g] = raw[(g * BM + r) * LDR + lane + 32];
-      }
-      __syncwarp();
       const int j0 = c0 + lane, j1 = j0 + 32;
       bool ok0 = r < nrows && j0 < hi && j0 <= pr, ok1 = r < nrows && j1 < hi && j1 <= pr;
       if (window > 0) {
         ok0 = ok0 && j0 > pr - window;
         ok1 = ok1 && j1 > pr - window;
       }
+      float mx[NHP];
+      {
+        float x0[NH], x1[NH];
 #pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        float s0, s1;
-        if (mix) {
-          s0 = 0.f;
-          s1 = 0.f;
-#pragma unroll
-          for (int g = 0; g < NH; ++g) {
-            const float w = mix_s[h * NH + g];
-            s0 = fmaf(w, x0[g], s0);
-            s1 = fmaf(w, x1[g], s1);
-          }
-        } else {
-          s0 = x0[h];
-          s1 = x1[h];
+        for (int g = 0; g < NH; ++g) {
+          x0[g] = raw[(g * BM + r) * LDR + lane];
+          x1[g] = raw[(g * BM + r) * LDR + lane + 32];
         }
-        s0 = ok0 ? s0 : -INFINITY;
-        s1 = ok1 ? s1 : -INFINITY;
-        const float mx = warp_max(fmaxf(s0, s1));
-        const float m_old = m_s[h * BM + r];
-        const float m_new = fmaxf(m_old, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float p0f = expf(s0 - m_use), p1f = expf(s1 - m_use);        // exp(-inf) = 0 for masked keys
-        const float sum = warp_sum(p0f + p1f);
         __syncwarp();
-        if (lane == 0) {
-          const float corr = expf(m_old - m_use);
-          corr_s[h * BM + r] = corr;
-          l_s[h * BM + r] = l_s[h * BM + r] * corr + sum;
-          m_s[h * BM + r] = m_new;
+        // the mixed scores go back to the row's place in shared memory; the largest of this lane's two per head stays
+#pragma unroll
+        for (int h = 0; h < NHP; ++h) {
+          float s0 = -INFINITY, s1 = -INFINITY;
+          if (h < NH) {
+            if (mix) {
+              s0 = 0.f;
+              s1 = 0.f;
+#pragma unroll
+              for (int g = 0; g < NH; ++g) {
+                const float w = mix_s[(h < NH ? h : 0) * NH + g];
+                s0 = fmaf(w, x0[g], s0);
+                s1 = fmaf(w, x1[g], s1);
+              }
+            } else {
+              s0 = x0[h < NH ? h : 0];
+              s1 = x1[h < NH ? h : 0];
+            }
+            s0 = ok0 ? s0 : -INFINITY;
+            s1 = ok1 ? s1 : -INFINITY;
+            raw[(h * BM + r) * LDR + lane] = s0;
+            raw[(h * BM + r) * LDR + lane + 32] = s1;
+          }
+          mx[h] = fmaxf(s0, s1);
         }
-        __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(raw + (h * BM + r) * LDR);
-        const __nv_bfloat16 h0 = __float2bfloat16_rn(p0f), h1 = __float2bfloat16_rn(p1f);
-        ph[lane] = h0;
-        ph[lane + 32] = h1;
-        ph[LDR + lane] = __float2bfloat16_rn(p0f - __bfloat162float(h0));
-        ph[LDR + lane + 32] = __float2bfloat16_rn(p1f - __bfloat162float(h1));
+      }
+      const float row_max = reduce_many<NHP, true>(mx, lane);
+      const int own = (lane >> OWNER_SHIFT) & (NHP - 1);          // the head this lane answers for
+      const bool owner = own < NH && (lane & ((1 << OWNER_SHIFT) - 1)) == 0;
+      float m_old_own = 0.f, m_use_own = 0.f;
+      if (owner) {
+        m_old_own = m_s[own * BM + r];
+        const float m_new = fmaxf(m_old_own, row_max);
+        m_use_own = (m_new == -INFINITY) ? 0.f : m_new;
+        m_s[own * BM + r] = m_new;
+      }
+      __syncwarp();
+      float psum[NHP];
+#pragma unroll
+      for (int h = 0; h < NHP; ++h) {
+        psum[h] = 0.f;
+        if (h < NH) {
+          const float m_new = m_s[h * BM + r];
+          const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+          const float p0f = expf(raw[(h * BM + r) * LDR + lane] - m_use);        // exp(-inf) = 0 for masked keys
+          const float p1f = expf(raw[(h * BM + r) * LDR + lane + 32] - m_use);
+          psum[h] = p0f + p1f;
+          __syncwarp();                                            // (all lanes have read the row's scores)
+          __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(raw + (h * BM + r) * LDR);
+          const __nv_bfloat16 h0 = __float2bfloat16_rn(p0f), h1 = __float2bfloat16_rn(p1f);
+          ph[lane] = h0;
+          ph[lane + 32] = h1;
+          ph[LDR + lane] = __float2bfloat16_rn(p0f - __bfloat162float(h0));
+          ph[LDR + lane + 32] = __float2bfloat16_rn(p1f - __bfloat162float(h1));
+        }
+      }
+      const float row_sum = reduce_many<NHP, false>(psum, lane);
+      if (owner) {
+        const float corr = expf(m_old_own - m_use_own);
+        corr_s[own * BM + r] = corr;
+        l_s[own * BM + r] = l_s[own * BM + r] * corr + row_sum;
       }
     }
     __syncthreads();
@@ -274,14 +373,14 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
     // ---- 3. O = O * correction + P V
 #pragma unroll
     for (int g = 0; g < NKV; ++g) {
-      for (int e = threadIdx.x; e < BN * (DV / 8); e += THREADS) {
-        const int seg = e % (DV / 8), key = e / (DV / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        const int off = off_s[key];
-        if (off >= 0) v = *reinterpret_cast<const uint4*>(v_pages + ((int64_t)off + (int64_t)g * page_size) * DV + seg * 8);
-        *reinterpret_cast<uint4*>(KVs + key * LDKV + seg * 8) = v;
-      }
+      if (g + 1 < NKV)
+        issue(c0, NKV + g + 1, cur);                              // the next kv head's values
+      else
+        issue(c0 + BN, 0, nxt);                                   // the next chunk's first keys
+      cp_async_wait<1>();
       __syncthreads();
+      const __nv_bfloat16* Vs = KVs + (used & 1) * BN * LDKV;
+      ++used;
 #pragma unroll
       for (int s = 0; s < TPG; ++s) {
         const int u = warp + WARPS * s;
@@ -297,7 +396,7 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
             O[g][s][n][3] *= c_hi;
           }
           const __nv_bfloat16* pbase = reinterpret_cast<const __nv_bfloat16*>(raw + (h * BM + (mat & 1) * 8 + r8) * LDR) + (mat >> 1) * 8;
-          const __nv_bfloat16* vbase = KVs + ((mat & 1) * 8 + r8) * LDKV + (mat >> 1) * 8 + db * 16;
+          const __nv_bfloat16* vbase = Vs + ((mat & 1) * 8 + r8) * LDKV + (mat >> 1) * 8 + db * 16;
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk) {
             uint32_t ah[4], al[4], b[4];
@@ -315,6 +414,7 @@ attention_mixed_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* 
     }
   }
 
+  cp_async_wait<0>();
   // ---- epilogue
   constexpr int n_out = NH * DV;
   if (nsplit > 1) {

@@ -137,7 +137,7 @@ class MixedHeadAttention(Mixer):
                 self.nh, self.nkv, self.dk, self.dv, len(self._thr_host), self.head_mixing, self.rt.dtype)
             if tc:      # CTAs are tiles of 16 tokens of one request
                 units = max(step.num_seqs, -(-step.num_tokens // 16))
-                plan = (True, native.attention_mixed_splits(units, longest, per_sm=1))
+                plan = (True, native.attention_mixed_splits(units, longest, per_sm=2, min_share=128))
             else:
                 plan = (False, native.attention_mixed_splits(step.num_tokens, longest))
             step.plans[key] = plan

@@ -76,7 +76,7 @@ def _run_attention(q, k, v, c, rel, talk, sink, dtype, page, cuts, eps=1e-5, val
                         cache.k_pages, cache.v_pages, cache.status)
         args = (H, G, dk, dv, c["scale"], 0, f32(rel), rows // 2, thr, f32(talk), f32(sink), c["q_temp"]["coef"], c["q_temp"]["every"])
         if kernel == "tc":
-            ns = nsplit or native.attention_mixed_splits(-(-n // 16), at + n, per_sm=1)        # (0: as the mixer chooses)
+            ns = nsplit or native.attention_mixed_splits(-(-n // 16), at + n, per_sm=2, min_share=128)        # (0: as the mixer chooses)
             scratch = torch.empty(native.attention_mixed_scratch_elems(n, H, dv, ns), dtype=torch.float32, device=DEV) if ns > 1 else None
             cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
             native.attention_mixed_tc(out[at:at + n], part, cache.k_pages, cache.v_pages, cache.table, pos, sot, cu, 1, *args, ns, scratch)
