@@ -1,6 +1,6 @@
 """Prefill and decode throughput of the Nurinex design beside Qwen3 dense at equal sizes.
 
-    python -m atom_b200.benchmarks.designs [--sizes 2048x16,4096x32] [--layers 4] [--prefill 2048]
+    python -m atom_b200.benchmarks.designs [--sizes 1024x8,2048x16] [--layers 4] [--prefill 2048]
                                            [--batch 8] [--context 2048] [--kernels]
 
 For each size (width x attention heads; head size 128, four query heads to a kv head, feed-forward three
@@ -138,7 +138,7 @@ def measure(cfg: dict, n_prefill: int, batch: int, context: int, kernels: bool) 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--sizes", default="2048x16,4096x32", help="comma-separated width x attention heads")
+    ap.add_argument("--sizes", default="1024x8,2048x16", help="comma-separated width x attention heads")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=8)

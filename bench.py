@@ -27,7 +27,7 @@ Every weight matrix of the model (tens of GB) is read in every step, far more th
 
 ``--designs`` leaves all of the above aside and prints the JSON line of ``atom_b200.benchmarks.designs``:
 prefill and decode throughput of the Nurinex design beside Qwen3 dense at equal layer sizes
-(``--designs 2048x16,4096x32``: width x attention heads; ``--designs-kernels`` adds every kernel's time).
+(``--designs 1024x8,2048x16``: width x attention heads; ``--designs-kernels`` adds every kernel's time).
 """
 from __future__ import annotations
 
@@ -180,7 +180,7 @@ def main() -> int:
     ap.add_argument("--only-measured-graphs", action="store_true",
                     help="capture only the decode graphs of the measured batch sizes and none for small mixed steps "
                          "(a short start-up, for runs under a profiler)")
-    ap.add_argument("--designs", nargs="?", const="2048x16,4096x32", default=None, metavar="SIZES",
+    ap.add_argument("--designs", nargs="?", const="1024x8,2048x16", default=None, metavar="SIZES",
                     help="instead of the default workload: Nurinex beside Qwen3 dense at these sizes (width x heads, ...)")
     ap.add_argument("--designs-kernels", action="store_true", help="with --designs: list every kernel's device time")
     args = ap.parse_args()
