@@ -134,6 +134,9 @@ ATT_CASES = [
     (16, 4, 64, 64, 24, 300.0, 0.4, 16, 16),
     (8, 8, 48, 80, 10, 64.0, 0.2, 3, 8),
     (16, 4, 128, 128, 32, 128.0, 0.5, 64, 16),
+    (12, 4, 32, 48, 6, 20.0, 0.3, 10, 16),
+    (6, 2, 64, 16, 14, 90.0, 0.6, 2, 8),
+    (5, 5, 16, 16, 8, 33.0, 0.1, 4, 4),
 ]
 
 
