@@ -7,8 +7,8 @@
 // the gate come from matrix products in the activation type.
 //
 // One block per (request, head); a state column j (the columns do not depend on one another) belongs to
-// kWkvSplit neighbouring lanes, each of which keeps a quarter of the column's key channels in registers, so
-// a token costs dk / 4 multiply-adds per thread and two shuffles, and the token-to-token chain is short.
+// SPLIT (8 or 4) neighbouring lanes, each of which keeps its share of the column's key channels in registers, so
+// a token costs dk / SPLIT multiply-adds per thread and log2 SPLIT shuffles, and the token-to-token chain is short.
 // The bonus needs no pass over the state: sum_i r[i] u[i] k[i] v[j] = v[j] * b with one number b per token,
 // which is formed while the chunk is staged.  Tokens go through shared memory in chunks of up to 32: r, k and
 // the decay of a chunk are converted (and the two exponentials taken) once, by all threads; the next chunk's
@@ -20,7 +20,6 @@
 namespace atom {
 
 constexpr int kWkvChunk = 32;     // most tokens staged at a time
-constexpr int kWkvSplit = 4;      // lanes to a state column
 constexpr int kWkvRegs = 8;       // elements of each staged array that a thread holds in flight
 
 // What a thread holds of the next chunk while the present one runs: the loads are issued before the
@@ -33,13 +32,13 @@ struct WkvStage {
 
 // TOK consecutive tokens of one state column's share of channels: all loads stand before the stores, so the
 // tokens' chains overlap (only S runs from token to token, one multiply-add each).  A lane's channels are the
-// float4 groups part, part + 4, part + 8, ...: the four lanes of a column read 64 consecutive bytes.
-template <int TOK, int DKP>
-__device__ __forceinline__ void wkv_tokens(float (&S)[DKP / kWkvSplit], const float* __restrict__ r_s,
+// float4 groups part, part + SPLIT, part + 2 SPLIT, ...: the lanes of a column read consecutive bytes.
+template <int TOK, int DKP, int SPLIT>
+__device__ __forceinline__ void wkv_tokens(float (&S)[DKP / SPLIT], const float* __restrict__ r_s,
                                            const float* __restrict__ k_s, const float* __restrict__ w_s,
                                            const float* __restrict__ v_s, const float* __restrict__ b_s,
                                            float* __restrict__ o_s, int c, int dv, int j, int part, unsigned group_mask) {
-  constexpr int DKQ = DKP / kWkvSplit;
+  constexpr int DKQ = DKP / SPLIT;
   float vj[TOK], acc[TOK][2];
 #pragma unroll
   for (int t = 0; t < TOK; ++t) {
@@ -52,7 +51,7 @@ __device__ __forceinline__ void wkv_tokens(float (&S)[DKP / kWkvSplit], const fl
     float4 r4[TOK], k4[TOK], w4[TOK];
 #pragma unroll
     for (int t = 0; t < TOK; ++t) {
-      const int at = (c + t) * DKP + (4 * m + part) * 4;
+      const int at = (c + t) * DKP + (SPLIT * m + part) * 4;
       r4[t] = *reinterpret_cast<const float4*>(r_s + at);
       k4[t] = *reinterpret_cast<const float4*>(k_s + at);
       w4[t] = *reinterpret_cast<const float4*>(w_s + at);
@@ -73,16 +72,16 @@ __device__ __forceinline__ void wkv_tokens(float (&S)[DKP / kWkvSplit], const fl
 #pragma unroll
   for (int t = 0; t < TOK; ++t) sum[t] = acc[t][0] + acc[t][1];
 #pragma unroll
-  for (int t = 0; t < TOK; ++t) sum[t] += __shfl_xor_sync(group_mask, sum[t], 1);      // (a column's lanes are neighbours)
+  for (int o = 1; o < SPLIT; o <<= 1)                             // (a column's lanes are neighbours in one warp)
 #pragma unroll
-  for (int t = 0; t < TOK; ++t) sum[t] += __shfl_xor_sync(group_mask, sum[t], 2);
+    for (int t = 0; t < TOK; ++t) sum[t] += __shfl_xor_sync(group_mask, sum[t], o);
   if (part == 0) {
 #pragma unroll
     for (int t = 0; t < TOK; ++t) o_s[(c + t) * dv + j] = fmaf(b_s[c + t], vj[t], sum[t]);
   }
 }
 
-template <typename T, int DKP>
+template <typename T, int DKP, int SPLIT>
 __global__ void __launch_bounds__(512)
 wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
            const void* __restrict__ d, int d_dtype, const T* __restrict__ gate, const void* __restrict__ w0,
@@ -91,7 +90,7 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
            float eps, int write_state, int chunk) {
   atom::pdl_trigger();
   atom::pdl_wait();
-  constexpr int DKQ = DKP / kWkvSplit;        // channels per lane (a multiple of 4)
+  constexpr int DKQ = DKP / SPLIT;        // channels per lane (a multiple of 4)
   extern __shared__ __align__(16) float smem[];
   float* r_s = smem;                          // [chunk][DKP]
   float* k_s = r_s + chunk * DKP;             // [chunk][DKP]
@@ -107,7 +106,7 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
   const int s = blockIdx.x, hd = blockIdx.y;
   const int t0 = cu_q[s], t1 = cu_q[s + 1];
   if (t1 <= t0) return;                       // a request without tokens in this step (padding)
-  const int j = threadIdx.x / kWkvSplit, part = threadIdx.x % kWkvSplit;
+  const int j = threadIdx.x / SPLIT, part = threadIdx.x % SPLIT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int64_t ldk = (int64_t)heads * dk, ldv = (int64_t)heads * dv;
   float* S_g = state + (((int64_t)state_slots[s] * heads + hd) * dk) * dv;
@@ -119,7 +118,7 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
   float S[DKQ];
 #pragma unroll
   for (int i = 0; i < DKQ; ++i) {
-    const int ch = ((i / 4) * kWkvSplit + part) * 4 + (i % 4);        // the channel that S[i] stands for
+    const int ch = ((i / 4) * SPLIT + part) * 4 + (i % 4);        // the channel that S[i] stands for
     S[i] = (ch < dk && j < dv) ? S_g[(int64_t)ch * dv + j] : 0.f;
   }
 
@@ -176,10 +175,10 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
     }
     __syncthreads();
     if (j < dv) {
-      const unsigned group_mask = 0xFu << (lane & ~3);
+      const unsigned group_mask = ((1u << SPLIT) - 1u) << (lane & ~(SPLIT - 1));
       int c = 0;
-      for (; c + 4 <= n; c += 4) wkv_tokens<4, DKP>(S, r_s, k_s, w_s, v_s, b_s, o_s, c, dv, j, part, group_mask);
-      for (; c < n; ++c) wkv_tokens<1, DKP>(S, r_s, k_s, w_s, v_s, b_s, o_s, c, dv, j, part, group_mask);
+      for (; c + 4 <= n; c += 4) wkv_tokens<4, DKP, SPLIT>(S, r_s, k_s, w_s, v_s, b_s, o_s, c, dv, j, part, group_mask);
+      for (; c < n; ++c) wkv_tokens<1, DKP, SPLIT>(S, r_s, k_s, w_s, v_s, b_s, o_s, c, dv, j, part, group_mask);
     }
     __syncthreads();
     // each head's o over its root mean square: a warp per token
@@ -200,7 +199,7 @@ wkv_kernel(T* __restrict__ y, const T* __restrict__ r, const T* __restrict__ k, 
   if (write_state && j < dv) {
 #pragma unroll
     for (int i = 0; i < DKQ; ++i) {
-      const int ch = ((i / 4) * kWkvSplit + part) * 4 + (i % 4);
+      const int ch = ((i / 4) * SPLIT + part) * 4 + (i % 4);
       if (ch < dk) S_g[(int64_t)ch * dv + j] = S[i];
     }
   }
@@ -211,34 +210,38 @@ static int launch_wkv(T* y, const T* r, const T* k, const T* v, const void* d, i
                       const void* w0, const void* u, const void* norm_w, int vec_dtype, float* state,
                       const int* cu_q, const int* state_slots, int S, int heads, int dk, int dv, float eps,
                       int write_state, cudaStream_t stream) {
-  const int threads = ((dv * kWkvSplit + 31) / 32) * 32;
-  const int dkp = ((dk + 15) / 16) * 16;
+  // eight lanes to a state column where that stays within 512 threads (more warps to hide the token-to-token
+  // latency behind, fewer channels per lane), else four
+  const int split = dv <= 64 ? 8 : 4;
+  const int threads = ((dv * split + 31) / 32) * 32;
+  const int dkp = ((dk + 4 * split - 1) / (4 * split)) * (4 * split);
   // as many tokens at a time as a thread's registers hold of every staged array
   int chunk = kWkvRegs * threads / (dkp > dv ? dkp : dv);
   chunk = chunk > kWkvChunk ? kWkvChunk : chunk;
   if (chunk < 1) return ATOM_ERR_ARG;
   const size_t smem = sizeof(float) * ((size_t)3 * chunk * dkp + 2 * dkp + (size_t)3 * chunk * dv);
-#define ATOM_WKV_CASE(N)                                                                                         \
-  case N:                                                                                                        \
-    if (smem > 48 * 1024)                                                                                        \
-      cudaFuncSetAttribute(wkv_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
-    launch_pdl(wkv_kernel<T, N>, dim3(S, heads), dim3(threads), smem, stream, y, r, k, v, d, d_dtype, gate, w0, \
-               u, norm_w, vec_dtype, state, cu_q, state_slots, heads, dk, dv, eps, write_state, chunk);          \
-    break;
-  switch (dkp) {
-    ATOM_WKV_CASE(16)
-    ATOM_WKV_CASE(32)
-    ATOM_WKV_CASE(48)
-    ATOM_WKV_CASE(64)
-    ATOM_WKV_CASE(80)
-    ATOM_WKV_CASE(96)
-    ATOM_WKV_CASE(112)
-    ATOM_WKV_CASE(128)
-    default:
-      return ATOM_ERR_ARG;
+#define ATOM_WKV_CASE(N, SP)                                                                                       \
+  if (dkp == N && split == SP) {                                                                                   \
+    if (smem > 48 * 1024)                                                                                          \
+      cudaFuncSetAttribute(wkv_kernel<T, N, SP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+    launch_pdl(wkv_kernel<T, N, SP>, dim3(S, heads), dim3(threads), smem, stream, y, r, k, v, d, d_dtype, gate,   \
+               w0, u, norm_w, vec_dtype, state, cu_q, state_slots, heads, dk, dv, eps, write_state, chunk);        \
+    return check_launch();                                                                                         \
   }
+  ATOM_WKV_CASE(32, 8)
+  ATOM_WKV_CASE(64, 8)
+  ATOM_WKV_CASE(96, 8)
+  ATOM_WKV_CASE(128, 8)
+  ATOM_WKV_CASE(16, 4)
+  ATOM_WKV_CASE(32, 4)
+  ATOM_WKV_CASE(48, 4)
+  ATOM_WKV_CASE(64, 4)
+  ATOM_WKV_CASE(80, 4)
+  ATOM_WKV_CASE(96, 4)
+  ATOM_WKV_CASE(112, 4)
+  ATOM_WKV_CASE(128, 4)
 #undef ATOM_WKV_CASE
-  return check_launch();
+  return ATOM_ERR_ARG;
 }
 
 }  // namespace atom

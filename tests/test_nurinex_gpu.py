@@ -679,3 +679,35 @@ def test_greedy_generation_bf16_with_preemption(dirs):
             row = logits[len(p) - 1 + i]
             assert row[tok] >= row.max() - 0.15, f"token {i}: logit {row[tok]:.3f} against {row.max():.3f}"
     eng.runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program_on_a_nurinex_folder(dirs, tmp_path, dtype):
+    """bin/trace_run as a user runs it (a child process, steps on standard input, one file of logits per step): the
+    model class is chosen by config.json; four state slots and a pool smaller than the requests' sum, so pages and
+    slots are used again."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    name = "Q"
+    seqs = _seqs(name)
+    steps, peak = traces.mixed(seqs, max_live=4, budget_tokens=320)
+    assert peak < sum(-(-len(t) // 64) * 64 for t in seqs.values())
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / f"out_{dtype}"
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", dirs[name], "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(peak)], input=text, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(l.split()[1]) for l in p.stdout.splitlines() if l.startswith("done ")] == [s["step"] for s in steps]
+    V = tn.CONFIGS[name]["vocab"]
+    outputs = {}
+    for s in steps:
+        n = sum(len(e["want"]) for e in s["entries"])
+        if n:
+            a = np.fromfile(out / f"{s['step']}.f32", dtype="<f4")
+            assert a.size == n * V
+            outputs[s["step"]] = a.reshape(n, V)
+    _compare(traces.collect(steps, outputs), _plain_logits(dirs[name], seqs), dtype, f"trace_run/{dtype}")
