@@ -137,6 +137,11 @@ ATT_CASES = [
     (12, 4, 32, 48, 6, 20.0, 0.3, 10, 16),
     (6, 2, 64, 16, 14, 90.0, 0.6, 2, 8),
     (5, 5, 16, 16, 8, 33.0, 0.1, 4, 4),
+    (16, 1, 64, 128, 16, 200.0, 0.5, 8, 16),
+    (8, 1, 128, 64, 20, 70.0, 0.3, 16, 32),
+    (2, 2, 256, 256, 8, 40.0, 0.2, 5, 16),
+    (16, 16, 32, 32, 8, 40.0, 0.2, 5, 16),
+    (32, 8, 32, 32, 12, 100.0, 0.4, 7, 16),
 ]
 
 
