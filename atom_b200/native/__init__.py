@@ -523,7 +523,8 @@ _workspaces = {}
 
 
 def _workspace(device: torch.device) -> torch.Tensor:
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    """The library's scratch memory: one per device and stream, since products on two streams may run at once."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
     ws = _workspaces.get(key)
     if ws is None:
         ws = torch.empty(32 << 20, dtype=torch.uint8, device=device)

@@ -67,10 +67,12 @@ class ParallelBlock:
         """The sum goes into the 32-bit residual here (a mixer that says ``adds_to_residual`` does it in
         its own last kernel), so there is nothing left for the next norm to add: returns None."""
         h = self.norm.add_norm(residual, delta, "norm.parallel")
-        f = self.ffn.forward(h, step) if self.ffn is not None else None
         if getattr(self.mixer, "adds_to_residual", False):
-            self.mixer.forward(h, step, cache, writes_cache, add_to=(residual, f))
+            # (the mixer calls the feed-forward when it suits it: beside a member that runs on a stream of its own)
+            ffn = (lambda: self.ffn.forward(h, step)) if self.ffn is not None else None
+            self.mixer.forward(h, step, cache, writes_cache, add_to=(residual, ffn))
         else:
+            f = self.ffn.forward(h, step) if self.ffn is not None else None
             m = self.mixer.forward(h, step, cache, writes_cache)
             native.pair_rmsnorm_add(residual[: m.shape[0]], m, None, None, None, f, 0.0)
         return None

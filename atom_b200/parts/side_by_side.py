@@ -6,7 +6,8 @@ The members are mixers of any registered kind, given as PartSpecs; their paramet
 steps is put together into one need (``CacheNeed.merged``: the pages of the one that keeps pages, every
 member's state arrays), and each member sees its own share of the run entry's cache slot.  An arrangement
 that adds the mixer's output to the residual stream anyway may pass ``add_to=(residual, extra)``: norms,
-average, the optional extra addend and the residual add are then one kernel in 32-bit.
+average, the optional extra addend and the residual add are then one kernel in 32-bit; ``extra`` may be a
+function that computes the addend, which then runs while the second member is busy on its own stream.
 """
 from __future__ import annotations
 
@@ -19,6 +20,10 @@ from . import registry
 from .base import Mixer
 from .registry import register
 from .spec import CacheNeed, ParamSpec, PartSpec
+
+
+# Rows of a step from which the second member runs on a stream of its own (0: never).
+OVERLAP_MIN_ROWS = 256
 
 
 def side_by_side_spec(hidden_size: int, norm_eps: float, members: Mapping[str, PartSpec],
@@ -43,6 +48,7 @@ class SideBySide(Mixer):
             raise ValueError("side_by_side takes exactly two members")
         self.hidden_size, self.norm_eps = hidden_size, norm_eps
         self.members = {n: registry.build("mixer", m) for n, m in members.items()}
+        self._side = None
 
     @property
     def graph_safe(self) -> bool:
@@ -73,12 +79,41 @@ class SideBySide(Mixer):
         for m in self.members.values():
             m.launch_plan(step)
 
+    def _members_forward(self, x, step, cache, writes_cache, meanwhile=None):
+        """Both members' outputs.  In an eager step of many rows the second member runs on a stream of its own
+        beside the first (and beside ``meanwhile``, work of the caller that reads the same rows): the two share
+        nothing but their input, and a member that cannot fill the device (a recurrence with one CTA per request
+        and head) would otherwise hold everything else up.  Captured steps keep to one stream."""
+        (na, ma), (nb, mb) = self.members.items()
+        T = x.shape[0]
+        if not (OVERLAP_MIN_ROWS and T >= OVERLAP_MIN_ROWS) or torch.cuda.is_current_stream_capturing():
+            a = ma.forward(x, step, cache.member(na), writes_cache)
+            b = mb.forward(x, step, cache.member(nb), writes_cache)
+            return (na, a), (nb, b), (meanwhile() if meanwhile is not None else None)
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device, priority=-1)     # its blocks are placed first
+        fork, join = torch.cuda.Event(), torch.cuda.Event()
+        fork.record(main)
+        self._side.wait_event(fork)
+        with torch.cuda.stream(self._side):
+            b = mb.forward(x, step, cache.member(nb), writes_cache)
+            join.record(self._side)
+        # the caller's work first: by the time the first member's long kernels take the SMs, the second member's
+        # chain of short ones has reached its own long kernel
+        extra = meanwhile() if meanwhile is not None else None
+        a = ma.forward(x, step, cache.member(na), writes_cache)
+        main.wait_event(join)
+        return (na, a), (nb, b), extra
+
     def forward(self, x, step, cache, writes_cache, add_to=None):
-        (na, a), (nb, b) = [(n, m.forward(x, step, cache.member(n), writes_cache)) for n, m in self.members.items()]
         if add_to is not None:
             residual, extra = add_to
+            (na, a), (nb, b), extra = self._members_forward(x, step, cache, writes_cache,
+                                                            extra if callable(extra) else (lambda: extra))
             native.pair_rmsnorm_add(residual, a, self._out_w[na], b, self._out_w[nb], extra, self.norm_eps)
             return None
+        (na, a), (nb, b), _ = self._members_forward(x, step, cache, writes_cache)
         T = x.shape[0]
         ws = self.rt.workspace
         acc = ws.get("sbs.acc", (T, self.hidden_size), torch.float32)

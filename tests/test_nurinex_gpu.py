@@ -716,3 +716,24 @@ def test_trace_run_program_on_a_nurinex_folder(dirs, tmp_path, dtype):
             assert a.size == n * V
             outputs[s["step"]] = a.reshape(n, V)
     _compare(traces.collect(steps, outputs), _plain_logits(dirs[name], seqs), dtype, f"trace_run/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_second_member_on_a_stream_of_its_own(dirs, name, dtype):
+    """Steps of many rows run the recurrence beside the attention and the feed-forward on two streams; forced here for
+    every eager step of two rows or more: whole prompts, portions, mixed steps, with pages and slots used again."""
+    from atom_b200.parts import side_by_side
+
+    seqs = _seqs(name)
+    ref = _plain_logits(dirs[name], seqs)
+    saved = side_by_side.OVERLAP_MIN_ROWS
+    try:
+        side_by_side.OVERLAP_MIN_ROWS = 2
+        runner = _runner(dirs[name], dtype, 320, tn.PAGE[name], max_num_seqs=4)
+        for what, steps in (("whole", traces.whole(seqs)), ("ragged", traces.ragged(seqs)),
+                            ("mixed", traces.mixed(seqs, max_live=4, budget_tokens=320)[0])):
+            _compare(traces.collect(steps, _replay(runner, steps)), ref, dtype, f"{name}/two streams/{what}")
+        assert any(getattr(b.mixer, "_side", None) is not None for b in runner.model.blocks), "no step used the second stream"
+    finally:
+        side_by_side.OVERLAP_MIN_ROWS = saved
