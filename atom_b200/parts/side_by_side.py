@@ -24,6 +24,7 @@ from .spec import CacheNeed, ParamSpec, PartSpec
 
 # Rows of a step from which the second member runs on a stream of its own (0: never).
 OVERLAP_MIN_ROWS = 256
+_side_streams = {}
 
 
 def side_by_side_spec(hidden_size: int, norm_eps: float, members: Mapping[str, PartSpec],
@@ -91,8 +92,11 @@ class SideBySide(Mixer):
             b = mb.forward(x, step, cache.member(nb), writes_cache)
             return (na, a), (nb, b), (meanwhile() if meanwhile is not None else None)
         main = torch.cuda.current_stream()
-        if self._side is None:
-            self._side = torch.cuda.Stream(device=x.device, priority=-1)     # its blocks are placed first
+        if self._side is None:      # one for all layers of a device: layers run one after another
+            key = x.device.index
+            if key not in _side_streams:
+                _side_streams[key] = torch.cuda.Stream(device=x.device, priority=-1)     # its blocks are placed first
+            self._side = _side_streams[key]
         fork, join = torch.cuda.Event(), torch.cuda.Event()
         fork.record(main)
         self._side.wait_event(fork)
