@@ -32,7 +32,7 @@ class Model:
                 raise ValueError(f"layer {i}: arrangement '{ls.arrangement}' has the parts {sorted(slots)}; "
                                  f"missing {absent}, not known {extra}")
             built = {n: registry.build(slots[n], ls.parts[n]) for n in slots if n in ls.parts}
-            self.blocks.append(arrangement(**built))
+            self.blocks.append(arrangement(**built, **dict(ls.args)))
             self._named += [(f"layers.{i}.{n}", built[n], ls.parts[n]) for n in slots if n in built]
         self.final_norm = registry.build("norm", spec.final_norm)
         self.lm_head = registry.build("head", spec.lm_head)
@@ -103,10 +103,22 @@ class Model:
         """step: StepContext; caches: cache slot -> CacheView.  Returns [R, vocab] float32."""
         residual = self.embedding.forward(step.token_ids, step.num_tokens)
         delta = None
+        scale = 1.0      # the factor with which the pending delta enters the residual (a block's ``delta_scale``)
         for e in self.spec.run_order:
             block = self.blocks[e.layer]
             if not getattr(block, "takes_pending", False):
                 delta = resolve(delta)      # (a block may hand its last product on unrun)
-            delta = block.run(residual, delta, step, caches.get(e.cache), e.writes_cache)
-        y = self.final_norm.add_norm(residual, resolve(delta), "norm.final", step.logits_rows, step.num_logits_rows)
+            if scale != 1.0 and delta is not None:
+                if hasattr(block, "delta_scale"):
+                    delta = block.run(residual, delta, step, caches.get(e.cache), e.writes_cache, delta_scale=scale)
+                else:
+                    raise ValueError("a block that scales its output is followed by one that cannot take the factor")
+            else:
+                delta = block.run(residual, delta, step, caches.get(e.cache), e.writes_cache)
+            scale = getattr(block, "delta_scale", 1.0)
+        if scale != 1.0:
+            y = self.final_norm.add_norm(residual, resolve(delta), "norm.final", step.logits_rows,
+                                         step.num_logits_rows, delta_scale=scale)
+        else:
+            y = self.final_norm.add_norm(residual, resolve(delta), "norm.final", step.logits_rows, step.num_logits_rows)
         return self.lm_head.forward(y, step.logits_out)

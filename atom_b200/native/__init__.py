@@ -67,7 +67,19 @@ _SIGNATURES = {
     "atom_attention_mixed": [_vp, _vp, _i64, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
                              _vp, _i, _vp, _i, _vp, _vp, _f, _i, _i, _vp, _vp],
     "atom_attention_mixed_merge": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
-    "atom_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp],
+    "atom_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _f, _vp],
+    "atom_latent_prepare": [_vp, _vp, _i, _i64, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _f, _vp, _f, _vp, _vp, _vp, _i, _i,
+                            _vp, _i64, _vp, _i, _vp],
+    "atom_rotate_pairs": [_vp, _i64, _i, _i, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp, _f, _vp, _vp, _i, _vp],
+    "atom_latent_attention_supports": [_i, _i, _i],
+    "atom_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp, _i, _vp],
+    "atom_causal_conv": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "atom_rglru_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f,
+                        _i, _vp],
+    "atom_sigmoid_mul": [_vp, _vp, _i, _i64, _i, _i, _vp],
+    "atom_gelu_mul": [_vp, _vp, _i, _i, _i, _vp],
+    "atom_gemm_f32_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _vp],
+    "atom_gemm_bf16_batched": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp],
     "atom_rmsnorm": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
     "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "atom_qknorm_rope_kvwrite": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i, _vp, _vp,
@@ -197,8 +209,8 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: 
 
 def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
-                n_rows: Optional[int] = None) -> None:
-    """residual (+= delta); out = rmsnorm(residual) * weight.  With ``rows`` (int32 indices)
+                n_rows: Optional[int] = None, delta_scale: float = 1.0) -> None:
+    """residual (+= delta_scale * delta); out = rmsnorm(residual) * weight.  With ``rows`` (int32 indices)
     only those rows are normalised, written densely to ``out``, and residual is left as is."""
     _cuda(out, residual, delta, weight, rows)
     H = residual.shape[-1]
@@ -208,7 +220,7 @@ def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: Optional[torch
     assert out.shape[0] >= n and out.shape[-1] == H
     _check(lib().atom_add_rmsnorm(out.data_ptr(), dtype_code(out.dtype), residual.data_ptr(),
                                   _ptr(delta), weight.data_ptr(), dtype_code(weight.dtype),
-                                  float(eps), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+                                  float(eps), _ptr(rows), n, H, float(delta_scale), _stream()), "add_rmsnorm")
 
 
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
@@ -543,6 +555,152 @@ def gemm_bf16(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
     _check(lib().atom_gemm_bf16(out.data_ptr(), dtype_code(out.dtype), a.data_ptr(), w.data_ptr(), M, N,
                                 K, a.stride(0), ws.data_ptr(), ws.numel(), _stream()), "gemm_bf16",
            own=False)
+
+
+def gemm_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[:, b, :] = a[:, b, :] @ w[b]^T for every b: a [M, B, K] and out [M, B, N] may be views (rows and
+    batches any distance apart, the last axis dense), w [B, N, K] dense.  bfloat16 operands through the GEMM library
+    with 32-bit sums (out bfloat16 or float32); float32 on the FMA kernel."""
+    _cuda(out, a, w)
+    M, B, K = a.shape
+    N = w.shape[1]
+    assert w.shape == (B, N, K) and out.shape == (M, B, N) and w.is_contiguous() and a.dtype == w.dtype
+    assert a.stride(2) == 1 and out.stride(2) == 1
+    if a.dtype == torch.float32:
+        assert out.dtype == torch.float32
+        _check(lib().atom_gemm_f32_batched(out.data_ptr(), a.data_ptr(), w.data_ptr(), B, M, N, K, a.stride(0),
+                                           out.stride(0), a.stride(1), N * K, out.stride(1), _stream()), "gemm_f32_batched")
+        return
+    assert a.dtype == torch.bfloat16
+    ws = _workspace(out.device)
+    _check(lib().atom_gemm_bf16_batched(out.data_ptr(), dtype_code(out.dtype), a.data_ptr(), w.data_ptr(), B, M, N, K,
+                                        a.stride(0), out.stride(0), a.stride(1), N * K, out.stride(1), ws.data_ptr(),
+                                        ws.numel(), _stream()), "gemm_bf16_batched", own=False)
+
+
+def latent_prepare(cq: torch.Tensor, proj: torch.Tensor, q_off: int, wq: torch.Tensor, eps: float,
+                   positions: torch.Tensor, seq_of_token: torch.Tensor, kv_off: int = 0, kv_rank: int = 0,
+                   rot_dim: int = 0, rot_dims: int = 0, wkv: Optional[torch.Tensor] = None,
+                   freq: Optional[torch.Tensor] = None, mag: float = 1.0, block_table: Optional[torch.Tensor] = None,
+                   page_size: int = 0, pages: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """Per token: cq = rmsnorm(proj[:, q_off : q_off + Rq]; wq); with ``pages``, the row [rmsnorm(first kv_rank
+    numbers at kv_off; wkv) | the next rot_dim numbers, the first rot_dims of them rotated by position * freq and
+    scaled by mag] goes to the token's place in the pages [pages, page size, kv_rank + rot_dim]."""
+    _cuda(cq, proj, wq, positions, seq_of_token, wkv, freq, block_table, pages, status)
+    T, Rq = cq.shape
+    assert proj.stride(1) == 1 and proj.dtype == cq.dtype and cq.is_contiguous() and wq.numel() == Rq
+    if pages is not None:
+        assert pages.dtype == proj.dtype and pages.is_contiguous() and tuple(pages.shape[1:]) == (page_size, kv_rank + rot_dim)
+        assert wkv.numel() == kv_rank and wkv.dtype == wq.dtype and freq.dtype == torch.float32 and freq.numel() >= rot_dims // 2
+        assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+    _check(lib().atom_latent_prepare(
+        cq.data_ptr(), proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), q_off, Rq, wq.data_ptr(), kv_off,
+        kv_rank, rot_dim, rot_dims, _ptr(wkv), dtype_code(wq.dtype), float(eps), _ptr(freq), float(mag),
+        positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table),
+        block_table.shape[1] if block_table is not None else 0, page_size, _ptr(pages),
+        pages.shape[0] if pages is not None else 0, _ptr(status), T, _stream()), "latent_prepare")
+
+
+def rotate_pairs(out: torch.Tensor, out_off: int, x: torch.Tensor, x_off: int, length: int, dims: int,
+                 freq: torch.Tensor, mag: float, positions: torch.Tensor, seq_of_token: torch.Tensor) -> None:
+    """For every token t and vector n: out[t, n, out_off : out_off + length] = x[t, n, x_off : x_off + length] with
+    its first ``dims`` numbers rotated (pairs (i, i + dims/2)) by positions[t] * freq[i], times mag.  out is float32."""
+    _cuda(out, x, freq, positions, seq_of_token)
+    T, n_vec = x.shape[0], x.shape[1]
+    assert out.dtype == torch.float32 and out.shape[:2] == x.shape[:2] and out.stride(2) == 1 and x.stride(2) == 1
+    assert freq.dtype == torch.float32 and freq.numel() >= dims // 2
+    _check(lib().atom_rotate_pairs(out.data_ptr(), out.stride(0), out.stride(1), out_off, x.data_ptr(),
+                                   dtype_code(x.dtype), x.stride(0), x.stride(1), x_off, n_vec, length, dims,
+                                   freq.data_ptr(), float(mag), positions.data_ptr(), seq_of_token.data_ptr(), T,
+                                   _stream()), "rotate_pairs")
+
+
+def latent_attention_supports(heads: int, kv_rank: int, rot_dim: int) -> bool:
+    return bool(lib().atom_latent_attention_supports(heads, kv_rank, rot_dim))
+
+
+def latent_attention_scratch_elems(T: int, heads: int, kv_rank: int, nsplit: int) -> int:
+    return T * heads * nsplit * (kv_rank + 2)
+
+
+def latent_attention(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                     positions: torch.Tensor, seq_of_token: torch.Tensor, kv_rank: int, rot_dim: int, scale: float,
+                     window: int, sink: Optional[torch.Tensor], nsplit: int = 1,
+                     scratch: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, :] = sum_j a[t, h, j] * pages[row(j)][:kv_rank], a the softmax over the keys j of the token's
+    request with 0 <= pos(t) - j < window (window 0: all) of scale * q[t, h] . pages[row(j)], with exp(sink[h])
+    one more term of the denominator.  q [T, heads, kv_rank + rot_dim] float32; pages [pages, page, kv_rank + rot_dim]."""
+    _cuda(out, q, pages, block_table, positions, seq_of_token, sink, scratch)
+    T, H, Dk = q.shape
+    assert q.dtype == torch.float32 and q.is_contiguous() and Dk == kv_rank + rot_dim
+    assert out.shape == (T, H, kv_rank) and out.is_contiguous() and out.dtype == pages.dtype
+    assert pages.is_contiguous() and pages.shape[2] == Dk and block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
+    assert nsplit == 1 or (scratch is not None and scratch.dtype == torch.float32
+                           and scratch.numel() >= latent_attention_scratch_elems(T, H, kv_rank, nsplit))
+    _check(lib().atom_latent_attention(out.data_ptr(), _ptr(scratch), q.data_ptr(), pages.data_ptr(),
+                                       dtype_code(pages.dtype), block_table.data_ptr(), block_table.shape[1],
+                                       pages.shape[1], positions.data_ptr(), seq_of_token.data_ptr(), T, H, kv_rank,
+                                       rot_dim, float(scale), int(window), _ptr(sink), nsplit, _stream()),
+           "latent_attention")
+    if nsplit > 1:
+        global launches
+        launches += 1
+
+
+def causal_conv(u: torch.Tensor, x: torch.Tensor, bx: torch.Tensor, w: torch.Tensor, bc: torch.Tensor,
+                conv_state: torch.Tensor, seq_of_token: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor) -> None:
+    """u[t, c] = bc[c] + sum_k w[c, k] * v[t - taps + 1 + k, c] within each request, v = x + bx; values before the
+    step's first token of a request come from its row of conv_state [slots, taps - 1, W] (read only)."""
+    _cuda(u, x, bx, w, bc, conv_state, seq_of_token, cu_q, state_slots)
+    T, W = u.shape
+    taps = w.shape[1]
+    assert x.shape == (T, W) and x.stride(1) == 1 and u.is_contiguous() and x.dtype == u.dtype == conv_state.dtype
+    assert w.shape == (W, taps) and w.is_contiguous() and bx.numel() == bc.numel() == W and bx.dtype == w.dtype == bc.dtype
+    assert conv_state.is_contiguous() and tuple(conv_state.shape[1:]) == (max(taps - 1, 0), W)
+    _check(lib().atom_causal_conv(u.data_ptr(), x.data_ptr(), dtype_code(x.dtype), x.stride(0), bx.data_ptr(),
+                                  w.data_ptr(), bc.data_ptr(), dtype_code(w.dtype), conv_state.data_ptr(),
+                                  seq_of_token.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), T, W, taps,
+                                  _stream()), "causal_conv")
+
+
+def rglru_scan(out: torch.Tensor, gates: torch.Tensor, gate_b: torch.Tensor, lam: torch.Tensor, u: torch.Tensor,
+               y: torch.Tensor, x: torch.Tensor, by: torch.Tensor, bx: torch.Tensor, state: torch.Tensor,
+               conv_state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, taps: int,
+               decay_c: float, write_state: bool = True) -> None:
+    """The gated linear recurrence of csrc/rglru.cu over every request's tokens of the step.  gates [T, blocks, 2 bw]
+    float32 (sums of r, then of i, per block), gate_b [blocks, 2 bw]; y, x [T, W] views of the branches before their
+    biases; state [slots, W] float32; conv_state [slots, taps - 1, W]."""
+    _cuda(out, gates, gate_b, lam, u, y, x, by, bx, state, conv_state, cu_q, state_slots)
+    T, W = out.shape
+    blocks, bw2 = gates.shape[1], gates.shape[2]
+    assert gates.dtype == torch.float32 and gates.is_contiguous() and blocks * bw2 == 2 * W and gate_b.numel() == 2 * W
+    assert u.shape == (T, W) and u.is_contiguous() and out.is_contiguous() and y.shape == x.shape == (T, W)
+    assert y.stride(1) == x.stride(1) == 1 and y.stride(0) == x.stride(0) and out.dtype == u.dtype == y.dtype == x.dtype
+    assert gate_b.dtype == lam.dtype == by.dtype == bx.dtype and gate_b.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == W
+    assert conv_state.dtype == out.dtype and conv_state.is_contiguous() and tuple(conv_state.shape[1:]) == (taps - 1, W)
+    _check(lib().atom_rglru_scan(out.data_ptr(), gates.data_ptr(), gate_b.data_ptr(), lam.data_ptr(), u.data_ptr(),
+                                 y.data_ptr(), x.data_ptr(), dtype_code(out.dtype), y.stride(0), by.data_ptr(),
+                                 bx.data_ptr(), dtype_code(lam.dtype), state.data_ptr(), conv_state.data_ptr(),
+                                 cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, W, bw2 // 2, taps, float(decay_c),
+                                 int(write_state), _stream()), "rglru_scan")
+
+
+def sigmoid_mul(x: torch.Tensor, g: torch.Tensor) -> None:
+    """x *= sigmoid(g) elementwise; x [T, n] dense, g [T, n] a view whose rows may lie further apart."""
+    _cuda(x, g)
+    assert x.shape == g.shape and x.dtype == g.dtype and x.is_contiguous() and g.stride(1) == 1
+    _check(lib().atom_sigmoid_mul(x.data_ptr(), g.data_ptr(), dtype_code(x.dtype), g.stride(0), x.shape[0], x.shape[1],
+                                  _stream()), "sigmoid_mul")
+
+
+def gelu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out = gelu_tanh(gate_up[:, :I]) * gate_up[:, I:]."""
+    _cuda(out, gate_up)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype
+    _check(lib().atom_gelu_mul(out.data_ptr(), gate_up.data_ptr(), dtype_code(out.dtype), T, I, _stream()), "gelu_mul")
 
 
 _device_flags = {}

@@ -55,6 +55,31 @@ ATOM_EXPORT int atom_gemm_bf16(void* C, int c_dtype, const void* A, const void* 
   return st == CUBLAS_STATUS_SUCCESS ? ATOM_OK : ATOM_ERR_LIB;
 }
 
+// B products at once (strided batch): C_b[M, N] = A_b[M, K] * W_b[N, K]^T, operand b of each kind
+// batch_* elements after the one before; rows of A_b lda apart, of C_b ldc apart, W_b dense.
+ATOM_EXPORT int atom_gemm_bf16_batched(void* C, int c_dtype, const void* A, const void* W, int B, int M, int N, int K,
+                                       int64_t lda, int64_t ldc, int64_t batch_a, int64_t batch_w, int64_t batch_c,
+                                       void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || B <= 0) return ATOM_OK;
+  if (K <= 0 || lda < K || ldc < N) return ATOM_ERR_ARG;
+  cublasHandle_t h = atom::handle_for_current_device();
+  if (h == nullptr) return ATOM_ERR_LIB;
+  if (cublasSetStream(h, stream) != CUBLAS_STATUS_SUCCESS) return ATOM_ERR_LIB;
+  if (workspace != nullptr &&
+      cublasSetWorkspace(h, workspace, workspace_bytes) != CUBLAS_STATUS_SUCCESS)
+    return ATOM_ERR_LIB;
+  const float alpha = 1.f, beta = 0.f;
+  cudaDataType ct;
+  if (c_dtype == ATOM_F32) ct = CUDA_R_32F;
+  else if (c_dtype == ATOM_BF16) ct = CUDA_R_16BF;
+  else return ATOM_ERR_ARG;
+  cublasStatus_t st = cublasGemmStridedBatchedEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, W, CUDA_R_16BF, K,
+                                                 (long long)batch_w, A, CUDA_R_16BF, (int)lda, (long long)batch_a,
+                                                 &beta, C, ct, (int)ldc, (long long)batch_c, B, CUBLAS_COMPUTE_32F,
+                                                 CUBLAS_GEMM_DEFAULT);
+  return st == CUBLAS_STATUS_SUCCESS ? ATOM_OK : ATOM_ERR_LIB;
+}
+
 ATOM_EXPORT int atom_add_bias(void* C, int c_dtype, const void* bias, int bias_dtype, int M, int N,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return ATOM_OK;

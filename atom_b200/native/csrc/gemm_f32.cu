@@ -10,7 +10,12 @@ constexpr int BM = 64, BN = 64, BK = 16;
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ W,
-                const float* __restrict__ bias, int M, int N, int K, int64_t lda, int64_t ldc) {
+                const float* __restrict__ bias, int M, int N, int K, int64_t lda, int64_t ldc,
+                int64_t batch_a, int64_t batch_w, int64_t batch_c) {
+  // blockIdx.z: one product of a batch, its operands batch_a / batch_w / batch_c elements after the one before
+  A += blockIdx.z * batch_a;
+  W += blockIdx.z * batch_w;
+  C += blockIdx.z * batch_c;
   atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
   __shared__ float As[BK][BM + 4];
@@ -69,6 +74,21 @@ ATOM_EXPORT int atom_gemm_f32(float* C, const float* A, const float* W, const fl
   if (K <= 0 || lda < K || ldc < N) return ATOM_ERR_ARG;
   dim3 grid((N + atom::BN - 1) / atom::BN, (M + atom::BM - 1) / atom::BM);
   if (grid.y > 65535) return ATOM_ERR_ARG;
-  atom::launch_pdl(atom::gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, C, A, W, bias, M, N, K, lda, ldc);
+  atom::launch_pdl(atom::gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, C, A, W, bias, M, N, K, lda, ldc, (int64_t)0,
+                   (int64_t)0, (int64_t)0);
+  return atom::check_launch();
+}
+
+// B products at once: C_b[M, N] = A_b[M, K] * W_b[N, K]^T with A_b = A + b * batch_a (rows lda apart),
+// W_b = W + b * batch_w (dense [N, K]), C_b = C + b * batch_c (rows ldc apart).
+ATOM_EXPORT int atom_gemm_f32_batched(float* C, const float* A, const float* W, int B, int M, int N, int K, int64_t lda,
+                                      int64_t ldc, int64_t batch_a, int64_t batch_w, int64_t batch_c,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || B <= 0) return ATOM_OK;
+  if (K <= 0 || lda < K || ldc < N || B > 65535) return ATOM_ERR_ARG;
+  dim3 grid((N + atom::BN - 1) / atom::BN, (M + atom::BM - 1) / atom::BM, B);
+  if (grid.y > 65535) return ATOM_ERR_ARG;
+  atom::launch_pdl(atom::gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, C, A, W, (const float*)nullptr, M, N, K, lda,
+                   ldc, batch_a, batch_w, batch_c);
   return atom::check_launch();
 }

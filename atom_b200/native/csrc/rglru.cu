@@ -1,0 +1,214 @@
+// A gated linear recurrence per channel with a short causal convolution in front (the recurrent block of
+// Griffin, De et al. 2024):
+//   v_t = x_t + bx                                   the branch's projection with its bias
+//   u_t = bc + sum_k w[c, k] * v_(t - taps + 1 + k)  causal convolution per channel, zeros before the start
+//   r_t = sigmoid(gr_t + br),  i_t = sigmoid(gi_t + bi)     gr, gi: block-diagonal products of u (computed outside)
+//   a_t = exp(-c * r_t * softplus(lam)),  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) * i_t * u_t
+//   out_t = S_t * gelu_tanh(y_t + by)
+// Per request the state row keeps S (32-bit) and the last taps - 1 values of v; both are zero at a request's
+// first token.  Gates, decay and state are 32-bit in both precisions.
+//
+//   causal_conv_kernel   every (token, channel) on its own: values before the step's first token come from
+//                        the state row, which this kernel only reads
+//   rglru_scan_kernel    one thread per (request, channel) walks the request's tokens of the step, then writes
+//                        S and the last taps - 1 values of v back
+#include "common.cuh"
+
+namespace atom {
+
+constexpr int kMaxTaps = 8;
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// The value of the x branch that enters the convolution, rounded as the state keeps it, so that a value is
+// the same whether it is read from this step's rows or, a step later, from the state.
+template <typename T>
+__device__ __forceinline__ float conv_input(const T* x, int64_t ld, int64_t t, int c, float bias) {
+  return to_float(from_float<T>(to_float(x[t * ld + c]) + bias));
+}
+
+// x: [T, ld] (the branch's columns start at x itself); u: [T, W]; conv_state: [slots, taps - 1, W], oldest first.
+template <typename T>
+__global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, int64_t ld,
+                                   const void* __restrict__ bx, const void* __restrict__ w,
+                                   const void* __restrict__ bc, int w_dtype, const T* __restrict__ conv_state,
+                                   const int* __restrict__ seq_of_token, const int* __restrict__ cu_q,
+                                   const int* __restrict__ state_slots, int W, int taps) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int t = blockIdx.x;
+  const int s = seq_of_token[t];
+  if (s < 0) return;
+  const int first = cu_q[s];
+  const T* st = conv_state + (int64_t)state_slots[s] * (taps - 1) * W;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
+    const float bias = load_as_float(bx, w_dtype, c);
+    float acc = load_as_float(bc, w_dtype, c);
+    for (int k = 0; k < taps; ++k) {
+      const int i = t - (taps - 1) + k;
+      const float v = i >= first ? conv_input(x, ld, i, c, bias) : to_float(st[(int64_t)(taps - 1 + i - first) * W + c]);
+      acc = fmaf(load_as_float(w, w_dtype, (int64_t)c * taps + k), v, acc);
+    }
+    u[(int64_t)t * W + c] = from_float<T>(acc);
+  }
+}
+
+// gates: [T, blocks, 2 * bw] float (r's sums, then i's, per block of bw channels); gate_b: [blocks, 2 * bw];
+// y, x: [T, ld] columns of the two branches before bias; out: [T, W].
+template <typename T>
+__global__ void rglru_scan_kernel(T* __restrict__ out, const float* __restrict__ gates, const void* __restrict__ gate_b,
+                                  const void* __restrict__ lam, const T* __restrict__ u, const T* __restrict__ y,
+                                  const T* __restrict__ x, int64_t ld, const void* __restrict__ by,
+                                  const void* __restrict__ bx, int w_dtype, float* __restrict__ state,
+                                  T* __restrict__ conv_state, const int* __restrict__ cu_q,
+                                  const int* __restrict__ state_slots, int W, int bw, int taps, float decay_c,
+                                  int write_state) {
+  atom::pdl_trigger();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const bool live = c < W;
+  const int b = live ? c / bw : 0, cb = live ? c - b * bw : 0;
+  float sp = 0.f, br = 0.f, bi = 0.f, byc = 0.f, bxc = 0.f;
+  if (live) {       // parameters do not depend on the kernels in front
+    sp = decay_c * softplus_f(load_as_float(lam, w_dtype, c));
+    br = load_as_float(gate_b, w_dtype, (int64_t)b * 2 * bw + cb);
+    bi = load_as_float(gate_b, w_dtype, (int64_t)b * 2 * bw + bw + cb);
+    byc = load_as_float(by, w_dtype, c);
+    bxc = load_as_float(bx, w_dtype, c);
+  }
+  atom::pdl_wait();
+  const int first = cu_q[s], last = cu_q[s + 1];
+  if (!live || last <= first) return;
+  const int slot = state_slots[s];
+  float S = state[(int64_t)slot * W + c];
+  const int64_t goff = (int64_t)b * 2 * bw + cb;
+  for (int t = first; t < last; ++t) {
+    const float* g = gates + (int64_t)t * 2 * W + goff;
+    const float r = sigmoid_f(g[0] + br), gi = sigmoid_f(g[bw] + bi);
+    const float uv = to_float(u[(int64_t)t * W + c]);
+    const float yv = gelu_tanh_f(to_float(y[(int64_t)t * ld + c]) + byc);
+    const float la = -r * sp;                        // log a
+    const float a = expf(la);
+    const float m = sqrtf(-expm1f(2.f * la));        // sqrt(1 - a^2) without cancellation near a = 1
+    S = fmaf(a, S, m * gi * uv);
+    out[(int64_t)t * W + c] = from_float<T>(S * yv);
+  }
+  if (!write_state) return;
+  state[(int64_t)slot * W + c] = S;
+  // the last taps - 1 convolution inputs: this step's where it has them, else the older ones moved up
+  T* st = conv_state + (int64_t)slot * (taps - 1) * W;
+  const int n = last - first, keep = taps - 1;
+  T old[kMaxTaps];
+  for (int k = 0; k < keep; ++k) old[k] = st[(int64_t)k * W + c];
+  for (int k = 0; k < keep; ++k) {
+    const int i = n - keep + k;       // index into this step's tokens of the request
+    st[(int64_t)k * W + c] = i >= 0 ? from_float<T>(to_float(x[(int64_t)(first + i) * ld + c]) + bxc) : old[k + n];
+  }
+}
+
+// x[t, :] *= sigmoid(g[t, :]) elementwise, x [T, n] dense, g rows ld apart; 32-bit arithmetic.
+template <typename T>
+__global__ void sigmoid_mul_kernel(T* __restrict__ x, const T* __restrict__ g, int64_t ld, int64_t total, int n) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const int64_t t = idx / n;
+    const int i = (int)(idx - t * n);
+    x[idx] = from_float<T>(to_float(x[idx]) * sigmoid_f(to_float(g[t * ld + i])));
+  }
+}
+
+// out[t, i] = gelu_tanh(gu[t, i]) * gu[t, I + i], gu [T, 2 I].
+template <typename T>
+__global__ void gelu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int I) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride) {
+    const int64_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    out[idx] = from_float<T>(gelu_tanh_f(to_float(gu[t * 2 * I + i])) * to_float(gu[t * 2 * I + I + i]));
+  }
+}
+
+}  // namespace atom
+
+ATOM_EXPORT int atom_causal_conv(void* u, const void* x, int dtype, int64_t ld, const void* bx, const void* w,
+                                 const void* bc, int w_dtype, const void* conv_state, const int* seq_of_token,
+                                 const int* cu_q, const int* state_slots, int T, int W, int taps, cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (W <= 0 || taps < 1 || taps > atom::kMaxTaps || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
+  const int threads = 128;
+  int gy = (W + threads - 1) / threads;
+  if (gy > 64) gy = 64;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::causal_conv_kernel<float>, dim3(T, gy), dim3(threads), 0, stream, (float*)u, (const float*)x,
+                     ld, bx, w, bc, w_dtype, (const float*)conv_state, seq_of_token, cu_q, state_slots, W, taps);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::causal_conv_kernel<__nv_bfloat16>, dim3(T, gy), dim3(threads), 0, stream, (__nv_bfloat16*)u,
+                     (const __nv_bfloat16*)x, ld, bx, w, bc, w_dtype, (const __nv_bfloat16*)conv_state, seq_of_token,
+                     cu_q, state_slots, W, taps);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
+ATOM_EXPORT int atom_rglru_scan(void* out, const float* gates, const void* gate_b, const void* lam, const void* u,
+                                const void* y, const void* x, int dtype, int64_t ld, const void* by, const void* bx,
+                                int w_dtype, float* state, void* conv_state, const int* cu_q, const int* state_slots,
+                                int num_seqs, int W, int bw, int taps, float decay_c, int write_state,
+                                cudaStream_t stream) {
+  if (num_seqs <= 0) return ATOM_OK;
+  if (W <= 0 || bw <= 0 || W % bw || taps < 1 || taps > atom::kMaxTaps || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16))
+    return ATOM_ERR_ARG;
+  const int threads = 64;
+  const dim3 grid(num_seqs, (W + threads - 1) / threads);
+  if (grid.y > 65535) return ATOM_ERR_ARG;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::rglru_scan_kernel<float>, grid, dim3(threads), 0, stream, (float*)out, gates, gate_b, lam,
+                     (const float*)u, (const float*)y, (const float*)x, ld, by, bx, w_dtype, state, (float*)conv_state,
+                     cu_q, state_slots, W, bw, taps, decay_c, write_state);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::rglru_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)out, gates,
+                     gate_b, lam, (const __nv_bfloat16*)u, (const __nv_bfloat16*)y, (const __nv_bfloat16*)x, ld, by, bx,
+                     w_dtype, state, (__nv_bfloat16*)conv_state, cu_q, state_slots, W, bw, taps, decay_c, write_state);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
+ATOM_EXPORT int atom_sigmoid_mul(void* x, const void* g, int dtype, int64_t ld, int T, int n, cudaStream_t stream) {
+  if (T <= 0 || n <= 0) return ATOM_OK;
+  const int64_t total = (int64_t)T * n;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::sigmoid_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)x, (const float*)g, ld, total, n);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::sigmoid_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ld, total, n);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
+ATOM_EXPORT int atom_gelu_mul(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (I <= 0) return ATOM_ERR_ARG;
+  const int64_t n = (int64_t)T * I;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::gelu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gu, n, I);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::gelu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}

@@ -1,5 +1,5 @@
 // Fused residual add + RMSNorm.
-//   r = residual[row] (+ delta[row]);  residual[row] = r  (unless rows are picked);
+//   r = residual[row] (+ dscale * delta[row]);  residual[row] = r  (unless rows are picked);
 //   out[i] = r * rsqrt(mean(r^2) + eps) * w
 // The residual stream and all arithmetic are 32-bit; `delta` (the previous block's
 // output) and `out` (the next matrix product's input) have the activation type.
@@ -12,7 +12,7 @@ namespace atom {
 template <typename TA>
 __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ residual,
                                    const TA* __restrict__ delta, const void* __restrict__ w,
-                                   int w_dtype, float eps, const int* __restrict__ rows, int H) {
+                                   int w_dtype, float eps, const int* __restrict__ rows, int H, float dscale) {
   atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
   __shared__ float scratch[32];
@@ -25,7 +25,7 @@ __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ res
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = res[i];
     if (d) {
-      v += to_float(d[i]);
+      v = fmaf(dscale, to_float(d[i]), v);
       // Picked rows are not carried further: their sum is formed again in the second pass
       // instead of being written back.
       if (!rows) res[i] = v;
@@ -36,7 +36,7 @@ __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ res
   const float rstd = rsqrtf(ss / (float)H + eps);
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = res[i];
-    if (d && rows) v += to_float(d[i]);
+    if (d && rows) v = fmaf(dscale, to_float(d[i]), v);
     o[i] = from_float<TA>(v * rstd * load_as_float(w, w_dtype, i));
   }
 }
@@ -69,7 +69,7 @@ template <int NV>
 __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual,
                                             const __nv_bfloat16* __restrict__ delta,
                                             const void* __restrict__ w, int w_dtype, float eps,
-                                            const int* __restrict__ rows, int H) {
+                                            const int* __restrict__ rows, int H, float dscale) {
   atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   __shared__ float scratch[32];
   const int r = blockIdx.x;
@@ -116,8 +116,8 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f = __bfloat1622float2(h[e]);
-          v[k][2 * e] += f.x;
-          v[k][2 * e + 1] += f.y;
+          v[k][2 * e] = fmaf(dscale, f.x, v[k][2 * e]);
+          v[k][2 * e + 1] = fmaf(dscale, f.y, v[k][2 * e + 1]);
         }
         if (!rows) {
           *reinterpret_cast<float4*>(res + i) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
@@ -201,7 +201,7 @@ ATOM_EXPORT int atom_pair_rmsnorm_add(float* residual, const void* a, const void
 
 ATOM_EXPORT int atom_add_rmsnorm(void* out, int act_dtype, float* residual, const void* delta,
                                  const void* w, int w_dtype, float eps, const int* rows, int n_rows,
-                                 int H, cudaStream_t stream) {
+                                 int H, float dscale, cudaStream_t stream) {
   if (n_rows <= 0) return ATOM_OK;
   if (H <= 0 || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
   const int threads = atom::norm_threads(H);
@@ -217,15 +217,15 @@ ATOM_EXPORT int atom_add_rmsnorm(void* out, int act_dtype, float* residual, cons
     }
     if (th < 64) th = 64;
     if (nv == 1)
-      atom::launch_pdl(atom::add_rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+      atom::launch_pdl(atom::add_rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H, dscale);
     else
-      atom::launch_pdl(atom::add_rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+      atom::launch_pdl(atom::add_rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H, dscale);
     return atom::check_launch();
   }
   if (act_dtype == ATOM_F32) {
-    atom::launch_pdl(atom::add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (float*)out, residual, (const float*)delta, w, w_dtype, eps, rows, H);
+    atom::launch_pdl(atom::add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (float*)out, residual, (const float*)delta, w, w_dtype, eps, rows, H, dscale);
   } else if (act_dtype == ATOM_BF16) {
-    atom::launch_pdl(atom::add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+    atom::launch_pdl(atom::add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H, dscale);
   } else {
     return ATOM_ERR_ARG;
   }

@@ -10,6 +10,11 @@ cache slot holds.
 sum; each sub-block's output is added to it inside the next norm's kernel:
    r += delta;  a = norm1(r);  m = mixer(a);  r += m;  b = norm2(r);  delta' = ffn(b).
 
+"prenorm_scaled" is "prenorm" with every sub-block's output entering the residual times a constant m, and with
+the feed-forward (and its norm) optional:
+   r += m * delta;  a = norm1(r);  x = mixer(a);  [r += m * x;  b = norm2(r);  x = ffn(b)]  -> x, added times m
+by whoever comes next (``delta_scale`` tells the model the factor of what ``run`` returned).
+
 "parallel" has one norm whose output both the mixer and the feed-forward read, and adds both to the residual:
    r += delta;  h = norm(r);  r += mixer(h) + ffn(h)        (a layer may have no feed-forward).
 
@@ -52,6 +57,30 @@ class PreNormBlock:
         m = _forward(self.mixer, a, step, cache, writes_cache)
         b = _add_norm(self.ffn_norm, residual, m, "norm.ffn", self.ffn)
         return _forward(self.ffn, b, step)
+
+
+@register("arrangement", "prenorm_scaled")
+class ScaledPreNormBlock:
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
+    optional = ("ffn_norm", "ffn")
+    takes_pending = False
+
+    def __init__(self, mixer_norm, mixer, ffn_norm=None, ffn=None, residual_mult: float = 1.0):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("prenorm_scaled: a feed-forward and its norm come together")
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.delta_scale = float(residual_mult)     # the factor of the output that run() hands on
+
+    def run(self, residual, delta, step, cache, writes_cache, delta_scale=None):
+        """delta_scale: the factor of the incoming delta (the block's own constant unless the model says otherwise)."""
+        m = self.delta_scale
+        a = self.mixer_norm.add_norm(residual, resolve(delta), "norm.mixer",
+                                     delta_scale=m if delta_scale is None else delta_scale)
+        x = self.mixer.forward(a, step, cache, writes_cache)
+        if self.ffn is None:
+            return x
+        b = self.ffn_norm.add_norm(residual, x, "norm.ffn", delta_scale=m)
+        return self.ffn.forward(b, step)
 
 
 @register("arrangement", "parallel")

@@ -1,0 +1,142 @@
+"""Attention through a latent: a token's keys and values are linear maps of one small normalised vector, which is
+all the cache keeps of it, beside a short rotated key part that every head shares.
+
+   [dq | dkv | g] = W_in h                              one product; dkv absent when another layer's cache is read
+   cq = rmsnorm(dq; w_dq),   q_h = W_uq,h cq = [qn_h (dim) | qr_h (rot_dim)],   qr_h rotated
+   c = rmsnorm(dkv[:kv_rank]; w_dkv),   kr = rotated dkv[kv_rank:]              the cached row is [c | kr]
+   s_h[i, j] = scale * (qn_h[i] . (W_uk,h c[j]) + qr_h[i] . kr[j])              0 <= i - j < window
+   a_h[i, j] = exp(s_h[i, j]) / (exp(sink_h) + sum_j' exp(s_h[i, j']))         (no sink term without sink)
+   y = W_o (concat_h(W_uv,h sum_j a_h[i, j] c[j]) * sigmoid(g))                 (no gate without gate)
+The key map is folded into the query, qn_h . (W_uk,h c) = (W_uk,h^T qn_h) . c, and the value map is applied after
+the weighted sum, so the attention kernel reads one row of kv_rank + rot_dim numbers per key for all heads and the
+keys and values of cached tokens are never rebuilt.  Rotation: the first ``rot_dims`` numbers of the rotated parts,
+pair (i, i + rot_dims/2), by the frequencies and the magnitude of the position part (parts/rope.py).
+
+A layer with ``reads_cache_of_other`` has no W_dkv: the run entry gives it the cache slot of the layer whose rows it
+reads (written earlier in the same step), with maps, queries, window, sink and gate of its own.  ``cache_window``
+is the window the cache has to keep for all its readers (None: every row).
+Folded queries, angles, scores, weights and sums are 32-bit in both precisions.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import native
+from . import registry
+from .base import Mixer
+from .linear import linear
+from .registry import register
+from .spec import CacheEntry, CacheNeed, ParamSpec, PartSpec
+
+
+@register("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, q_rank: int,
+                 kv_rank: int, scale: float, norm_eps: float, position: PartSpec, window: Optional[int] = None,
+                 cache_window: Optional[int] = None, sink: bool = False, gate: bool = False,
+                 reads_cache_of_other: bool = False):
+        self.hidden_size, self.nh, self.dn, self.rd, self.dv = hidden_size, num_heads, head_dim, rot_dim, value_dim
+        self.q_rank, self.R, self.scale, self.norm_eps = q_rank, kv_rank, float(scale), norm_eps
+        self.window, self.cache_window = window, cache_window
+        self.sink, self.gate, self.borrows = sink, gate, reads_cache_of_other
+        self.position = registry.build("position", position)
+        if self.position.rotary_dim > rot_dim:
+            raise ValueError(f"latent_attention: {self.position.rotary_dim} rotated numbers in a part of {rot_dim}")
+        if window is not None and (cache_window is not None and cache_window < window):
+            raise ValueError("latent_attention: the cache keeps fewer rows than the window looks back")
+        if not native_supports(num_heads, kv_rank, rot_dim):
+            raise ValueError(f"latent_attention: kv_rank {kv_rank} + rot_dim {rot_dim} is beyond what the kernel takes")
+        self._sink = self._ukT = self._uv = self._freq = None
+
+    def _in_rows(self):
+        rows = [self.q_rank]
+        if not self.borrows:
+            rows.append(self.R + self.rd)
+        if self.gate:
+            rows.append(self.nh * self.dv)
+        return tuple(rows)
+
+    def params(self) -> Dict[str, ParamSpec]:
+        H, W = self.nh, self.hidden_size
+        rows = self._in_rows()
+        p = {
+            "in.weight": ParamSpec((sum(rows), W), rows=rows),
+            "dq.norm": ParamSpec((self.q_rank,), role="vector", init="norm"),
+            "uq.weight": ParamSpec((H * (self.dn + self.rd), self.q_rank)),
+            "uk.weight": ParamSpec((H * self.dn, self.R)),
+            "uv.weight": ParamSpec((H * self.dv, self.R)),
+            "o.weight": ParamSpec((W, H * self.dv)),
+        }
+        if not self.borrows:
+            p["dkv.norm"] = ParamSpec((self.R,), role="vector", init="norm")
+        if self.sink:
+            p["sink"] = ParamSpec((H,), role="vector", init="normal")
+        return p
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("pages", window=self.cache_window, entries=(CacheEntry("latent", (self.R + self.rd,)),))
+
+    def after_load(self) -> None:
+        H = self.nh
+        self._sink = self.w_sink.float().contiguous() if self.sink else None
+        # W_uk,h^T as the matrix of the folded query's product: [H, kv_rank, dim]
+        self._ukT = self.w_uk_weight.view(H, self.dn, self.R).transpose(1, 2).contiguous()
+        self._uv = self.w_uv_weight.view(H, self.dv, self.R)
+        self._freq = self.position.frequencies(self.rt)
+
+    def launch_plan(self, step):
+        """Into how many shares every token's keys are cut: a CTA is a token and a group of heads."""
+        key = ("latent_attention", self.nh, self.R, self.rd, self.window or 0)
+        plan = step.plans.get(key)
+        if plan is None:
+            longest = min(step.max_ctx_len, self.window) if self.window else step.max_ctx_len
+            plan = step.plans[key] = native.attention_mixed_splits(step.num_tokens, longest)
+        return plan
+
+    def forward(self, x, step, cache, writes_cache):
+        T = x.shape[0]
+        ws, dt = self.rt.workspace, self.rt.dtype
+        H, dn, rd, dv, R, Rq = self.nh, self.dn, self.rd, self.dv, self.R, self.q_rank
+        rows = self._in_rows()
+        proj = linear(x, self.w_in_weight, None, ws.get("lat.in", (T, sum(rows)), dt))
+        bt = step.block_tables[cache.group]
+        pages = cache.pages["latent"]
+        cq = ws.get("lat.cq", (T, Rq), dt)
+        pos = self.position
+        if self.borrows or not writes_cache:
+            native.latent_prepare(cq, proj, 0, self.w_dq_norm, self.norm_eps, step.positions, step.seq_of_token)
+        else:
+            native.latent_prepare(cq, proj, 0, self.w_dq_norm, self.norm_eps, step.positions, step.seq_of_token,
+                                  kv_off=Rq, kv_rank=R, rot_dim=rd, rot_dims=pos.rotary_dim, wkv=self.w_dkv_norm,
+                                  freq=self._freq, mag=pos.magnitude, block_table=bt, page_size=cache.page_size,
+                                  pages=pages, status=step.status)
+        q = linear(cq, self.w_uq_weight, None, ws.get("lat.q", (T, H * (dn + rd)), dt)).view(T, H, dn + rd)
+        qf = ws.get("lat.qf", (T, H, R + rd), torch.float32)
+        native.gemm_batched(qf[:, :, :R], q[:, :, :dn], self._ukT)
+        native.rotate_pairs(qf, R, q, dn, rd, pos.rotary_dim, self._freq, pos.magnitude, step.positions,
+                            step.seq_of_token)
+        olat = ws.get("lat.olat", (T, H, R), dt)
+        nsplit = self.launch_plan(step)
+        scratch = None
+        if nsplit > 1:
+            scratch = ws.get("lat.splits", (native.latent_attention_scratch_elems(T, H, R, nsplit),), torch.float32)
+        native.latent_attention(olat, qf, pages, bt, step.positions, step.seq_of_token, R, rd, self.scale,
+                                self.window or 0, self._sink, nsplit, scratch)
+        heads = ws.get("lat.heads", (T, H, dv), dt)
+        native.gemm_batched(heads, olat, self._uv)
+        heads = heads.view(T, H * dv)
+        if self.gate:
+            g_off = sum(rows) - H * dv
+            native.sigmoid_mul(heads, proj[:, g_off:])
+        return linear(heads, self.w_o_weight, None, ws.get("lat.out", (T, self.hidden_size), dt))
+
+
+def native_supports(heads: int, kv_rank: int, rot_dim: int) -> bool:
+    """Sizes the attention kernel takes; asked without loading the library where there is no device."""
+    if not torch.cuda.is_available():
+        return heads > 0 and kv_rank > 0 and rot_dim >= 0
+    return native.latent_attention_supports(heads, kv_rank, rot_dim)

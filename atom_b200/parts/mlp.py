@@ -2,7 +2,8 @@
    gu = x W_gate_up^T;  f = silu(gu[:, :I]) * gu[:, I:];  y = f W_down^T.
 Dense with the xIELU activation:  y = W_down act(W_up x),
    act(z) = softplus(p) z^2 + z/2 for z > 0,  (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 otherwise,
-with the two numbers (p, q) a parameter of the layer."""
+with the two numbers (p, q) a parameter of the layer.
+GELU-gated:  y = W_down (gelu_tanh(W_gate x) * (W_up x)),  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))."""
 from __future__ import annotations
 
 import math
@@ -40,6 +41,26 @@ class GatedSiluMLP(FeedForward):
         if defer and may_defer(f, self.w_down_weight):
             return PendingProduct(f, self.w_down_weight, None, out)
         return linear(f, self.w_down_weight, None, out)
+
+
+@register("ffn", "gated_gelu")
+class GatedGeluMLP(FeedForward):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+
+    def params(self) -> Dict[str, ParamSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return {"gate_up.weight": ParamSpec((2 * I, H), rows=(I, I)), "down.weight": ParamSpec((H, I))}
+
+    def forward(self, x, step):
+        T = x.shape[0]
+        ws, dt = self.rt.workspace, self.rt.dtype
+        gu = linear(x, self.w_gate_up_weight, None, ws.get("ffn.gate_up", (T, 2 * self.intermediate_size), dt))
+        f = ws.get("ffn.act", (T, self.intermediate_size), dt)
+        native.gelu_mul(f, gu)
+        return linear(f, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))
 
 
 @register("ffn", "dense_xielu")

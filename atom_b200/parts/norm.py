@@ -33,9 +33,11 @@ class RMSNorm(Norm):
 
     fuses_products = True      # add_norm takes a PendingProduct as delta and the keyword scaled_ok
 
-    def add_norm(self, residual, delta, tag, rows=None, n_rows=None, scaled_ok=False):
+    def add_norm(self, residual, delta, tag, rows=None, n_rows=None, scaled_ok=False, delta_scale=1.0):
+        """delta_scale: what is added to the residual is delta_scale * delta (a design whose sub-blocks enter the
+        residual stream times a constant); the product epilogue has no such factor, so nothing is folded then."""
         if isinstance(delta, PendingProduct):
-            if scaled_ok and rows is None and self._folds(residual, delta):
+            if scaled_ok and rows is None and delta_scale == 1.0 and self._folds(residual, delta):
                 M, ws = residual.shape[0], self.rt.workspace
                 xw = ws.get(tag + ".scaled", (M, self.size), torch.bfloat16)
                 ssq = ws.get(tag + ".ssq", (native.gemm_rows_grid(), 16), torch.float32)
@@ -44,7 +46,7 @@ class RMSNorm(Norm):
             delta = delta.run()
         n = residual.shape[0] if rows is None else (rows.numel() if n_rows is None else n_rows)
         out = self.rt.workspace.get(tag, (n, self.size), self.rt.dtype)
-        native.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows, n)
+        native.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows, n, delta_scale)
         return out
 
     def _folds(self, residual, p: PendingProduct) -> bool:

@@ -35,6 +35,59 @@ class RotaryNeox(PositionEncoding):
         return self._table
 
 
+def yarn_frequencies(rotary_dim: int, theta: float, factor: float, original: float, fast: float, slow: float):
+    """Frequencies of the rotary pairs stretched for sequences longer than ``original`` positions (YaRN, Peng et al.
+    2023), and the factor on cos and sin.  With f_i = theta^(-2i / d) and pair(n) = d ln(original / (2 pi n)) /
+    (2 ln theta) the pair whose wave makes n turns over the original length: pairs below lo = floor(pair(fast)) keep
+    f_i, pairs above hi = ceil(pair(slow)) get f_i / factor, and between them the two are blended linearly.
+    Computed in 64-bit."""
+    import math
+
+    half = rotary_dim // 2
+    f = [theta ** (-2.0 * i / rotary_dim) for i in range(half)]
+
+    def pair(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair(fast)), 0)
+    hi = min(math.ceil(pair(slow)), rotary_dim - 1)
+    out = []
+    for i in range(half):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f[i] / factor * ramp + f[i] * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+@register("position", "rope_yarn")
+class RotaryYarn(PositionEncoding):
+    """Half-split rotary pairs whose angle is computed in the kernel, position * frequency in 32-bit, from a vector
+    of frequencies (so no table bounds the positions), with YaRN's stretch when ``scaling`` is given as
+    {factor, original, fast, slow}.  A mixer asks for ``frequencies(rt)`` and ``magnitude`` and hands them to its
+    kernel; ``table`` gives None."""
+    graph_safe = True
+
+    def __init__(self, rotary_dim: int, theta: float, scaling: Optional[dict] = None):
+        if rotary_dim % 2:
+            raise ValueError("rotary_dim must be even")
+        self.rotary_dim, self.theta = rotary_dim, float(theta)
+        if scaling:
+            self._f, self.magnitude = yarn_frequencies(rotary_dim, self.theta, float(scaling["factor"]),
+                                                       float(scaling["original"]), float(scaling["fast"]),
+                                                       float(scaling["slow"]))
+        else:
+            self._f, self.magnitude = [self.theta ** (-2.0 * i / rotary_dim) for i in range(rotary_dim // 2)], 1.0
+        self._dev: Optional[torch.Tensor] = None
+
+    def frequencies(self, rt: Runtime) -> torch.Tensor:
+        """[rotary_dim / 2] float32 on the device (at least one element, so that it always has an address)."""
+        if self._dev is None or self._dev.device != rt.device:
+            self._dev = torch.tensor(self._f or [0.0], dtype=torch.float64).to(torch.float32).to(rt.device)
+        return self._dev
+
+    def apply(self, q, k, step) -> None:
+        raise NotImplementedError("rope_yarn is applied by mixers that take frequencies (latent_attention)")
+
+
 @register("position", "none")
 class NoPosition(PositionEncoding):
     graph_safe = True

@@ -59,6 +59,8 @@ class LayerSpec:
 
     arrangement: str
     parts: Mapping[str, PartSpec]
+    # constants of the arrangement itself (keyword arguments of its constructor beside the parts)
+    args: Mapping[str, Any] = field(default_factory=dict)
 
     def __hash__(self):
         return hash((self.arrangement, tuple(sorted(self.parts))))
