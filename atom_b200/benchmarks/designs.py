@@ -1,12 +1,15 @@
-"""Prefill and decode throughput of the Nurinex design beside Qwen3 dense at equal sizes.
+"""Prefill and decode throughput of the Nurinex and Mugulorn designs beside Qwen3 dense at equal sizes.
 
     python -m atom_b200.benchmarks.designs [--sizes 1024x8,2048x16] [--layers 4] [--prefill 2048]
-                                           [--batch 8] [--context 2048] [--kernels]
+                                           [--batch 8] [--context 2048] [--kernels] [--only qwen3,mugulorn]
 
 For each size (width x attention heads; head size 128, four query heads to a kv head, feed-forward three
 times the width, vocabulary 32768) two engines are built with random bfloat16 weights and the same number
 of layers: Qwen3 dense, and Nurinex whose attention has the same heads and whose recurrence has width / 64
-heads of 64 channels.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
+heads of 64 channels; and Mugulorn, whose layers alternate attention through a latent (the same heads,
+128 + 64 numbers per head, values of 128, a latent of width / 4, queries through width / 2, a window of 1024;
+every second attention layer reads the cache of the one before) with a gated linear recurrence of the width's
+channels in as many blocks as heads behind a convolution of 4 taps.  Measured on the device with CUDA events: one prompt of ``--prefill`` tokens through
 one step, and decode steps of ``--batch`` requests whose caches hold ``--context`` tokens (captured graphs,
 as the engine runs them).  With ``--kernels`` the kernels of one prefill step and of one decode step are
 listed with their summed device time (the engine's profiler hook), which is what the per-kernel rooflines
@@ -42,6 +45,30 @@ def nurinex_config(width: int, heads: int, layers: int) -> dict:
     layer = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": 3 * width}}
     return {"architecture": "Nurinex", "vocab": VOCAB, "width": width, "embedding": {"scale": 1.0},
             "norm": {"eps": 1e-5}, "layers": [layer] * layers}
+
+
+def mugulorn_config(width: int, heads: int, layers: int) -> dict:
+    def att(kv_from=None):
+        m = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width // 2, "kv_rank": width // 4,
+             "scale": 192 ** -0.5, "mask": {"size": 1024},
+             "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": 3 * width}}
+
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": heads, "conv": 4}, "mlp": {"kind": "dense", "ff": 3 * width}}
+    out, owner = [], None
+    for i in range(layers):
+        if i % 2:
+            out.append(rec)
+        elif owner is None:
+            out.append(att())
+            owner = i
+        else:
+            out.append(att(kv_from=owner))
+            owner = None
+    return {"architecture": "Mugulorn", "vocab": VOCAB, "width": width, "residual_mult": 0.5, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "layers": out}
 
 
 def _runner(cfg: dict, pages: int, max_len: int, batch: int):
@@ -144,14 +171,19 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--kernels", action="store_true", help="list the kernels of one prefill and one decode step")
+    ap.add_argument("--only", default="qwen3,nurinex,mugulorn", help="the designs to measure, comma-separated")
     args = ap.parse_args(argv)
+    configs = {"qwen3": qwen3_config, "nurinex": nurinex_config, "mugulorn": mugulorn_config}
+    chosen = [d for d in args.only.split(",") if d]
+    if any(d not in configs for d in chosen):
+        ap.error(f"--only takes {sorted(configs)}")
     results: List[dict] = []
     for item in args.sizes.split(","):
         width, heads = (int(x) for x in item.lower().split("x"))
         row = {"width": width, "heads": heads, "kv_heads": max(1, heads // 4), "head_dim": 128, "ff": 3 * width,
                "layers": args.layers}
-        row["qwen3"] = measure(qwen3_config(width, heads, args.layers), args.prefill, args.batch, args.context, args.kernels)
-        row["nurinex"] = measure(nurinex_config(width, heads, args.layers), args.prefill, args.batch, args.context, args.kernels)
+        for d in chosen:
+            row[d] = measure(configs[d](width, heads, args.layers), args.prefill, args.batch, args.context, args.kernels)
         results.append(row)
     print(json.dumps({"bench": "designs", "dtype": "bf16", "data": "synthetic", "prefill_tokens": args.prefill,
                       "decode_batch": args.batch, "decode_context": args.context, "vocab": VOCAB, "sizes": results}))

@@ -26,8 +26,9 @@ Every weight matrix of the model (tens of GB) is read in every step, far more th
 126 MB L2 holds, so consecutive timed steps do not find their inputs in L2.
 
 ``--designs`` leaves all of the above aside and prints the JSON line of ``atom_b200.benchmarks.designs``:
-prefill and decode throughput of the Nurinex design beside Qwen3 dense at equal layer sizes
-(``--designs 1024x8,2048x16``: width x attention heads; ``--designs-kernels`` adds every kernel's time).
+prefill and decode throughput of the Nurinex and Mugulorn designs beside Qwen3 dense at equal layer sizes
+(``--designs 1024x8,2048x16``: width x attention heads; ``--designs-kernels`` adds every kernel's time;
+``--designs-only qwen3,mugulorn`` measures some of the designs).
 """
 from __future__ import annotations
 
@@ -181,13 +182,16 @@ def main() -> int:
                     help="capture only the decode graphs of the measured batch sizes and none for small mixed steps "
                          "(a short start-up, for runs under a profiler)")
     ap.add_argument("--designs", nargs="?", const="1024x8,2048x16", default=None, metavar="SIZES",
-                    help="instead of the default workload: Nurinex beside Qwen3 dense at these sizes (width x heads, ...)")
+                    help="instead of the default workload: Nurinex and Mugulorn beside Qwen3 dense at these sizes "
+                         "(width x heads, ...)")
+    ap.add_argument("--designs-only", default=None, metavar="NAMES", help="with --designs: only these designs (qwen3,nurinex,mugulorn)")
     ap.add_argument("--designs-kernels", action="store_true", help="with --designs: list every kernel's device time")
     args = ap.parse_args()
 
     if args.designs is not None:
         from atom_b200.benchmarks import designs
-        return designs.main(["--sizes", args.designs] + (["--kernels"] if args.designs_kernels else []))
+        return designs.main(["--sizes", args.designs] + (["--kernels"] if args.designs_kernels else [])
+                            + (["--only", args.designs_only] if args.designs_only else []))
     if args.impl == "reference":
         print(json.dumps(reference_arm()))
         return 0
