@@ -72,10 +72,13 @@ _SIGNATURES = {
                             _vp, _i64, _vp, _i, _vp],
     "atom_rotate_pairs": [_vp, _i64, _i, _i, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp, _f, _vp, _vp, _i, _vp],
     "atom_latent_attention_supports": [_i, _i, _i],
+    "atom_latent_attention_head_group": [_i, _i, _i],
     "atom_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp, _i, _vp],
+    "atom_latent_attention_tc_supports": [_i, _i, _i],
+    "atom_latent_attention_tc": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "atom_causal_conv": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "atom_rglru_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f,
-                        _i, _vp],
+    "atom_rglru_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                        _f, _i, _vp],
     "atom_sigmoid_mul": [_vp, _vp, _i, _i64, _i, _i, _vp],
     "atom_gelu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "atom_gemm_f32_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _vp],
@@ -619,6 +622,11 @@ def latent_attention_supports(heads: int, kv_rank: int, rot_dim: int) -> bool:
     return bool(lib().atom_latent_attention_supports(heads, kv_rank, rot_dim))
 
 
+def latent_attention_head_group(heads: int, kv_rank: int, rot_dim: int) -> int:
+    """Heads that a CTA of the plain kernel takes together."""
+    return max(1, int(lib().atom_latent_attention_head_group(heads, kv_rank, rot_dim)))
+
+
 def latent_attention_scratch_elems(T: int, heads: int, kv_rank: int, nsplit: int) -> int:
     return T * heads * nsplit * (kv_rank + 2)
 
@@ -646,6 +654,30 @@ def latent_attention(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, bl
     if nsplit > 1:
         global launches
         launches += 1
+
+
+LATENT_TC = True      # False: the plain kernel also where the tensor-core kernel takes the sizes (measurements, tests)
+
+
+def latent_attention_tc_supports(heads: int, kv_rank: int, rot_dim: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().atom_latent_attention_tc_supports(heads, kv_rank, rot_dim))
+
+
+def latent_attention_tc(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                        positions: torch.Tensor, cu_q: torch.Tensor, num_seqs: int, kv_rank: int, rot_dim: int,
+                        scale: float, window: int, sink: Optional[torch.Tensor]) -> None:
+    """``latent_attention`` on the tensor cores (bfloat16 pages and output): a CTA is a few consecutive tokens of a
+    request with a group of heads, found from cu_q on the device."""
+    _cuda(out, q, pages, block_table, positions, cu_q, sink)
+    T, H, Dk = q.shape
+    assert q.dtype == torch.float32 and q.is_contiguous() and Dk == kv_rank + rot_dim
+    assert out.shape == (T, H, kv_rank) and out.is_contiguous() and out.dtype == pages.dtype == torch.bfloat16
+    assert pages.is_contiguous() and pages.shape[2] == Dk and block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
+    _check(lib().atom_latent_attention_tc(out.data_ptr(), q.data_ptr(), pages.data_ptr(), block_table.data_ptr(),
+                                          block_table.shape[1], pages.shape[1], cu_q.data_ptr(), positions.data_ptr(),
+                                          num_seqs, T, H, kv_rank, rot_dim, float(scale), int(window), _ptr(sink),
+                                          _stream()), "latent_attention_tc")
 
 
 def causal_conv(u: torch.Tensor, x: torch.Tensor, bx: torch.Tensor, w: torch.Tensor, bc: torch.Tensor,
@@ -683,7 +715,7 @@ def rglru_scan(out: torch.Tensor, gates: torch.Tensor, gate_b: torch.Tensor, lam
     _check(lib().atom_rglru_scan(out.data_ptr(), gates.data_ptr(), gate_b.data_ptr(), lam.data_ptr(), u.data_ptr(),
                                  y.data_ptr(), x.data_ptr(), dtype_code(out.dtype), y.stride(0), by.data_ptr(),
                                  bx.data_ptr(), dtype_code(lam.dtype), state.data_ptr(), conv_state.data_ptr(),
-                                 cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, W, bw2 // 2, taps, float(decay_c),
+                                 cu_q.data_ptr(), state_slots.data_ptr(), num_seqs, T, W, bw2 // 2, taps, float(decay_c),
                                  int(write_state), _stream()), "rglru_scan")
 
 

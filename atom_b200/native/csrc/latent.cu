@@ -321,6 +321,11 @@ ATOM_EXPORT int atom_rotate_pairs(float* out, int64_t out_ld, int out_stride, in
   return atom::check_launch();
 }
 
+ATOM_EXPORT int atom_latent_attention_head_group(int H, int R, int rd) {
+  if (H <= 0 || R <= 0 || rd < 0) return 0;
+  return atom::latent_head_group(H, R, rd);
+}
+
 ATOM_EXPORT int atom_latent_attention_supports(int H, int R, int rd) {
   if (H <= 0 || R <= 0 || rd < 0) return 0;
   const int hg = atom::latent_head_group(H, R, rd);

@@ -10,8 +10,8 @@
 //
 //   causal_conv_kernel   every (token, channel) on its own: values before the step's first token come from
 //                        the state row, which this kernel only reads
-//   rglru_scan_kernel    one thread per (request, channel) walks the request's tokens of the step, then writes
-//                        S and the last taps - 1 values of v back
+//   rglru_scan_kernel    a request's tokens of the step in runs, one warp per run and one lane per channel; then S
+//                        and the last taps - 1 values of v go back to the state row
 #include "common.cuh"
 
 namespace atom {
@@ -61,17 +61,24 @@ __global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, i
 
 // gates: [T, blocks, 2 * bw] float (r's sums, then i's, per block of bw channels); gate_b: [blocks, 2 * bw];
 // y, x: [T, ld] columns of the two branches before bias; out: [T, W].
+// A block is 32 channels (the lanes) x NW warps; a request's tokens of the step are cut into NW runs, one per warp.
+// The recurrence is linear in S, so a run is summed up as S_end = A S_begin + B: every warp first finds (A, B) of its
+// run, the pairs of the runs before it give its S_begin, and a second walk writes the outputs.  Few tokens (a decoded
+// token above all) are walked once, by the first warp.
+constexpr int kScanOnce = 8;      // up to this many tokens of a request: one walk
+
 template <typename T>
-__global__ void rglru_scan_kernel(T* __restrict__ out, const float* __restrict__ gates, const void* __restrict__ gate_b,
-                                  const void* __restrict__ lam, const T* __restrict__ u, const T* __restrict__ y,
-                                  const T* __restrict__ x, int64_t ld, const void* __restrict__ by,
-                                  const void* __restrict__ bx, int w_dtype, float* __restrict__ state,
-                                  T* __restrict__ conv_state, const int* __restrict__ cu_q,
-                                  const int* __restrict__ state_slots, int W, int bw, int taps, float decay_c,
-                                  int write_state) {
+__global__ void __launch_bounds__(1024)
+rglru_scan_kernel(T* __restrict__ out, const float* __restrict__ gates, const void* __restrict__ gate_b,
+                  const void* __restrict__ lam, const T* __restrict__ u, const T* __restrict__ y,
+                  const T* __restrict__ x, int64_t ld, const void* __restrict__ by, const void* __restrict__ bx,
+                  int w_dtype, float* __restrict__ state, T* __restrict__ conv_state, const int* __restrict__ cu_q,
+                  const int* __restrict__ state_slots, int W, int bw, int taps, float decay_c, int write_state) {
   atom::pdl_trigger();
+  __shared__ float sA[32][33], sB[32][33];
   const int s = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
+  const int c = blockIdx.y * 32 + lane;
   const bool live = c < W;
   const int b = live ? c / bw : 0, cb = live ? c - b * bw : 0;
   float sp = 0.f, br = 0.f, bi = 0.f, byc = 0.f, bxc = 0.f;
@@ -84,26 +91,51 @@ __global__ void rglru_scan_kernel(T* __restrict__ out, const float* __restrict__
   }
   atom::pdl_wait();
   const int first = cu_q[s], last = cu_q[s + 1];
-  if (!live || last <= first) return;
+  const int n = last - first;
+  if (n <= 0) return;
+  const bool once = n <= kScanOnce || NW == 1;
+  const int per = once ? n : (n + NW - 1) / NW;
+  const int t0 = min(last, first + warp * per), t1 = min(last, t0 + per);
   const int slot = state_slots[s];
-  float S = state[(int64_t)slot * W + c];
   const int64_t goff = (int64_t)b * 2 * bw + cb;
-  for (int t = first; t < last; ++t) {
+
+  // a_t and b_t = sqrt(1 - a_t^2) i_t u_t of token t
+  auto step_of = [&](int t, float& a, float& bt) {
     const float* g = gates + (int64_t)t * 2 * W + goff;
     const float r = sigmoid_f(g[0] + br), gi = sigmoid_f(g[bw] + bi);
-    const float uv = to_float(u[(int64_t)t * W + c]);
+    const float la = -r * sp;                            // log a
+    a = expf(la);
+    bt = sqrtf(-expm1f(2.f * la)) * gi * to_float(u[(int64_t)t * W + c]);      // sqrt(1 - a^2) without cancellation near a = 1
+  };
+
+  float S = live ? state[(int64_t)slot * W + c] : 0.f;
+  if (!once) {
+    float A = 1.f, B = 0.f;
+    if (live)
+      for (int t = t0; t < t1; ++t) {
+        float a, bt;
+        step_of(t, a, bt);
+        A *= a;
+        B = fmaf(a, B, bt);
+      }
+    sA[warp][lane] = A;
+    sB[warp][lane] = B;
+    __syncthreads();
+    for (int k = 0; k < warp; ++k) S = fmaf(sA[k][lane], S, sB[k][lane]);
+  }
+  if (!live) return;
+  for (int t = t0; t < t1; ++t) {
+    float a, bt;
+    step_of(t, a, bt);
+    S = fmaf(a, S, bt);
     const float yv = gelu_tanh_f(to_float(y[(int64_t)t * ld + c]) + byc);
-    const float la = -r * sp;                        // log a
-    const float a = expf(la);
-    const float m = sqrtf(-expm1f(2.f * la));        // sqrt(1 - a^2) without cancellation near a = 1
-    S = fmaf(a, S, m * gi * uv);
     out[(int64_t)t * W + c] = from_float<T>(S * yv);
   }
-  if (!write_state) return;
+  if (!write_state || t1 != last || t0 >= t1) return;       // the warp with the request's last token carries on
   state[(int64_t)slot * W + c] = S;
   // the last taps - 1 convolution inputs: this step's where it has them, else the older ones moved up
   T* st = conv_state + (int64_t)slot * (taps - 1) * W;
-  const int n = last - first, keep = taps - 1;
+  const int keep = taps - 1;
   T old[kMaxTaps];
   for (int k = 0; k < keep; ++k) old[k] = st[(int64_t)k * W + c];
   for (int k = 0; k < keep; ++k) {
@@ -163,13 +195,14 @@ ATOM_EXPORT int atom_causal_conv(void* u, const void* x, int dtype, int64_t ld, 
 ATOM_EXPORT int atom_rglru_scan(void* out, const float* gates, const void* gate_b, const void* lam, const void* u,
                                 const void* y, const void* x, int dtype, int64_t ld, const void* by, const void* bx,
                                 int w_dtype, float* state, void* conv_state, const int* cu_q, const int* state_slots,
-                                int num_seqs, int W, int bw, int taps, float decay_c, int write_state,
+                                int num_seqs, int T, int W, int bw, int taps, float decay_c, int write_state,
                                 cudaStream_t stream) {
-  if (num_seqs <= 0) return ATOM_OK;
+  if (num_seqs <= 0 || T <= 0) return ATOM_OK;
   if (W <= 0 || bw <= 0 || W % bw || taps < 1 || taps > atom::kMaxTaps || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16))
     return ATOM_ERR_ARG;
-  const int threads = 64;
-  const dim3 grid(num_seqs, (W + threads - 1) / threads);
+  // warps along the tokens: by the step's size alone, so that a captured step replays the same launch
+  const int threads = 32 * (T >= 512 ? 32 : (T >= 32 ? 8 : 1));
+  const dim3 grid(num_seqs, (W + 31) / 32);
   if (grid.y > 65535) return ATOM_ERR_ARG;
   if (dtype == ATOM_F32)
     atom::launch_pdl(atom::rglru_scan_kernel<float>, grid, dim3(threads), 0, stream, (float*)out, gates, gate_b, lam,

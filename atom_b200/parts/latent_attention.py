@@ -31,6 +31,9 @@ from .registry import register
 from .spec import CacheEntry, CacheNeed, ParamSpec, PartSpec
 
 
+TC_MIN_TOKENS = 32     # steps with a portion and at least this many tokens run on the tensor-core kernel
+
+
 @register("mixer", "latent_attention")
 class LatentAttention(Mixer):
     graph_safe = True
@@ -89,12 +92,18 @@ class LatentAttention(Mixer):
         self._freq = self.position.frequencies(self.rt)
 
     def launch_plan(self, step):
-        """Into how many shares every token's keys are cut: a CTA is a token and a group of heads."""
+        """(whether the tensor-core kernel runs, into how many shares the plain kernel cuts every token's keys).  The
+        tensor-core kernel's CTA is a few consecutive tokens of a request, so it pays in steps with prompt portions;
+        in a step of single tokens the plain kernel, a CTA per token and group of heads, shares out the keys."""
         key = ("latent_attention", self.nh, self.R, self.rd, self.window or 0)
         plan = step.plans.get(key)
         if plan is None:
             longest = min(step.max_ctx_len, self.window) if self.window else step.max_ctx_len
-            plan = step.plans[key] = native.attention_mixed_splits(step.num_tokens, longest)
+            tc = (native.LATENT_TC and step.max_q_len > 1 and step.num_tokens >= TC_MIN_TOKENS
+                  and native.latent_attention_tc_supports(self.nh, self.R, self.rd, self.rt.dtype))
+            groups = -(-self.nh // native.latent_attention_head_group(self.nh, self.R, self.rd))
+            plan = step.plans[key] = (tc, 1 if tc else native.attention_mixed_splits(step.num_tokens * groups, longest,
+                                                                                     per_sm=2, min_share=64))
         return plan
 
     def forward(self, x, step, cache, writes_cache):
@@ -120,12 +129,16 @@ class LatentAttention(Mixer):
         native.rotate_pairs(qf, R, q, dn, rd, pos.rotary_dim, self._freq, pos.magnitude, step.positions,
                             step.seq_of_token)
         olat = ws.get("lat.olat", (T, H, R), dt)
-        nsplit = self.launch_plan(step)
-        scratch = None
-        if nsplit > 1:
-            scratch = ws.get("lat.splits", (native.latent_attention_scratch_elems(T, H, R, nsplit),), torch.float32)
-        native.latent_attention(olat, qf, pages, bt, step.positions, step.seq_of_token, R, rd, self.scale,
-                                self.window or 0, self._sink, nsplit, scratch)
+        tc, nsplit = self.launch_plan(step)
+        if tc:
+            native.latent_attention_tc(olat, qf, pages, bt, step.positions, step.cu_q, step.num_seqs, R, rd, self.scale,
+                                       self.window or 0, self._sink)
+        else:
+            scratch = None
+            if nsplit > 1:
+                scratch = ws.get("lat.splits", (native.latent_attention_scratch_elems(T, H, R, nsplit),), torch.float32)
+            native.latent_attention(olat, qf, pages, bt, step.positions, step.seq_of_token, R, rd, self.scale,
+                                    self.window or 0, self._sink, nsplit, scratch)
         heads = ws.get("lat.heads", (T, H, dv), dt)
         native.gemm_batched(heads, olat, self._uv)
         heads = heads.view(T, H * dv)

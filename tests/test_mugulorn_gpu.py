@@ -104,7 +104,7 @@ def _plain_latent_scores(q, rows, R, scale, window, sink):
     return torch.einsum("hij,jd->ihd", a, rows[:, :R])
 
 
-def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0):
+def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0, kernel="plain"):
     from atom_b200 import native
 
     T, H, _ = q.shape
@@ -121,8 +121,12 @@ def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0
         ns = nsplit or native.attention_mixed_splits(n, min(at + n, window) if window else at + n)
         scratch = torch.empty(native.latent_attention_scratch_elems(n, H, R, ns), dtype=torch.float32, device=DEV) if ns > 1 else None
         o = torch.zeros(n, H, R, dtype=dt, device=DEV)
-        native.latent_attention(o, q[at:at + n].float().contiguous().to(DEV), cache.pages, cache.table,
-                                _i32(range(at, at + n)), _i32([0] * n), R, rd, scale, window, sk, ns, scratch)
+        if kernel == "tc":
+            native.latent_attention_tc(o, q[at:at + n].float().contiguous().to(DEV), cache.pages, cache.table,
+                                       _i32(range(at, at + n)), _i32([0, n]), 1, R, rd, scale, window, sk)
+        else:
+            native.latent_attention(o, q[at:at + n].float().contiguous().to(DEV), cache.pages, cache.table,
+                                    _i32(range(at, at + n)), _i32([0] * n), R, rd, scale, window, sk, ns, scratch)
         out[at:at + n] = o
         at += n
     assert at == T
@@ -131,8 +135,15 @@ def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0
 
 LATENT_CASES = [  # H, R, rd, window, page, T
     (4, 32, 8, 24, 16, 70), (2, 48, 16, 7, 8, 40), (3, 16, 4, 0, 8, 100), (5, 36, 12, 1, 16, 20), (1, 60, 20, 33, 16, 90),
-    (8, 128, 32, 128, 32, 300), (16, 512, 64, 64, 64, 130),
+    (8, 128, 32, 128, 32, 300), (16, 512, 64, 64, 64, 130), (6, 64, 16, 50, 16, 170), (3, 256, 0, 0, 16, 150),
+    (70, 64, 32, 40, 8, 90),
 ]
+
+
+def _kernels(H, R, rd, dtype):
+    """The kernels that take these sizes: the plain one always, the tensor-core one where it does."""
+    from atom_b200 import native
+    return ["plain", "tc"] if native.latent_attention_tc_supports(H, R, rd, _dt(dtype)) else ["plain"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -145,9 +156,10 @@ def test_latent_attention_in_prompts_portions_and_decoding(case, dtype):
     sink = torch.randn(H, generator=g).double()
     scale = 2.0 / (R + rd) ** 0.5
     want = _plain_latent_scores(q.float().double(), rows, R, scale, window, sink)
-    for cuts in ([T], [T - 9] + [1] * 9, [13, 5, 2, 29, 2, 8, 3, 17] * 8):
-        got = _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts)
-        _close(got, want, dtype, f"cuts {cuts[:3]}", f32=2e-5, bf16=1e-2)
+    for kernel in _kernels(H, R, rd, dtype):
+        for cuts in ([T], [T - 9] + [1] * 9, [13, 5, 2, 29, 2, 8, 3, 17] * 8):
+            got = _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, kernel=kernel)
+            _close(got, want, dtype, f"{kernel}, cuts {cuts[:3]}", f32=2e-5, bf16=1e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -171,7 +183,7 @@ def test_one_key_at_the_windows_edge_stands_out(window, dtype):
     """One key row carries a mark that only it has and a score far above all others.  Queries at distance window - 1
     find the mark, queries at distance window do not: in a prompt, across portions that end at every place around
     the edge and a page's border, and decoded one by one."""
-    H, R, rd, page, T = 2, 16, 4, 16, 420
+    H, R, rd, page, T = 2, 64, 16, 16, 420
     needle = 77
     g = torch.Generator().manual_seed(window)
     rows = torch.randn(T, R + rd, generator=g) * 0.1
@@ -190,24 +202,29 @@ def test_one_key_at_the_windows_edge_stands_out(window, dtype):
     edge = needle + window
     for cuts in ([T], [edge - 1, 1, 1, 1, T], [edge, T], [edge + 1, T], [needle + 1] + [1] * (T - needle - 1) if window <= 64 else [T],
                  [needle, 2, window, 2, T]):
-        got = _run_latent(q, rows, R, rd, 1.0, window, sink, dtype, page, cuts)
-        assert all(float(got[p, :, 0].min()) > 0.9 for p in inside), f"window {window}, cuts {cuts[:4]}: a key inside is lost"
-        assert all(float(got[p, :, 0].abs().max()) == 0 for p in outside), f"window {window}, cuts {cuts[:4]}: a key outside is seen"
-        _close(got, want, dtype, f"window {window}", f32=2e-5, bf16=1e-2)
+        for kernel in _kernels(H, R, rd, dtype):
+            if kernel == "tc" and len(cuts) > 20:
+                continue
+            got = _run_latent(q, rows, R, rd, 1.0, window, sink, dtype, page, cuts, kernel=kernel)
+            what = f"{kernel}, window {window}, cuts {cuts[:4]}"
+            assert all(float(got[p, :, 0].min()) > 0.9 for p in inside), f"{what}: a key inside is lost"
+            assert all(float(got[p, :, 0].abs().max()) == 0 for p in outside), f"{what}: a key outside is seen"
+            _close(got, want, dtype, what, f32=2e-5, bf16=1e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sink_counts_once_has_no_value_and_is_not_scaled(dtype):
     """With one key, the weight of its row is 1 / (1 + exp(sink - score)); a large sink empties the output."""
-    H, R, rd = 3, 8, 4
+    H, R, rd = 3, 64, 16
     rows = _rounded(torch.ones(1, R + rd), dtype)
     q = torch.zeros(1, H, R + rd).double()
     q[:, :, 0] = torch.tensor([0.0, 1.0, -2.0]).double()
     sink = torch.tensor([0.0, 3.0, 40.0]).double()
     scale = 0.5
-    got = _run_latent(q, rows, R, rd, scale, 5, sink, dtype, 8, [1])
     want = 1.0 / (1.0 + torch.exp(sink - scale * q[0, :, 0]))
-    _close(got[0, :, 0], want, dtype, "sink", scale=1.0, f32=1e-6, bf16=4e-3)
+    for kernel in _kernels(H, R, rd, dtype):
+        got = _run_latent(q, rows, R, rd, scale, 5, sink, dtype, 8, [1], kernel=kernel)
+        _close(got[0, :, 0], want, dtype, f"sink, {kernel}", scale=1.0, f32=1e-6, bf16=4e-3)
     none = _run_latent(q, rows, R, rd, scale, 5, None, dtype, 8, [1])
     _close(none[0, :, 0], torch.ones(H).double(), dtype, "no sink", scale=1.0)
 
