@@ -75,7 +75,8 @@ _SIGNATURES = {
     "atom_latent_attention_head_group": [_i, _i, _i],
     "atom_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp, _i, _vp],
     "atom_latent_attention_tc_supports": [_i, _i, _i],
-    "atom_latent_attention_tc": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "atom_latent_attention_tc": [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _i, _vp],
+    "atom_latent_merge": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp],
     "atom_causal_conv": [_vp, _vp, _i, _i64, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "atom_rglru_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                         _f, _i, _vp],
@@ -663,12 +664,22 @@ def latent_attention_tc_supports(heads: int, kv_rank: int, rot_dim: int, dtype: 
     return dtype == torch.bfloat16 and bool(lib().atom_latent_attention_tc_supports(heads, kv_rank, rot_dim))
 
 
+def latent_attention_tc_tile_tokens(heads: int, rows: int = 64) -> int:
+    """Consecutive tokens of a request in one tile of the tensor-core kernel (``rows`` = tokens x heads)."""
+    return max(1, rows // min(heads, rows))
+
+
 def latent_attention_tc(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                         positions: torch.Tensor, cu_q: torch.Tensor, num_seqs: int, kv_rank: int, rot_dim: int,
-                        scale: float, window: int, sink: Optional[torch.Tensor]) -> None:
+                        scale: float, window: int, sink: Optional[torch.Tensor], nsplit: int = 1,
+                        scratch: Optional[torch.Tensor] = None, seq_of_token: Optional[torch.Tensor] = None,
+                        rows: int = 64) -> None:
     """``latent_attention`` on the tensor cores (bfloat16 pages and output): a CTA is a few consecutive tokens of a
-    request with a group of heads, found from cu_q on the device."""
-    _cuda(out, q, pages, block_table, positions, cu_q, sink)
+    request with a group of heads (``rows`` = 64 query rows, or 16 for steps of single tokens), found from cu_q on
+    the device.  With ``nsplit`` > 1 every CTA walks one share of
+    its tokens' keys and the merge kernel puts the shares together (``scratch`` as for the plain kernel;
+    ``seq_of_token`` marks padding rows)."""
+    _cuda(out, q, pages, block_table, positions, cu_q, sink, scratch, seq_of_token)
     T, H, Dk = q.shape
     assert q.dtype == torch.float32 and q.is_contiguous() and Dk == kv_rank + rot_dim
     assert out.shape == (T, H, kv_rank) and out.is_contiguous() and out.dtype == pages.dtype == torch.bfloat16
@@ -677,7 +688,12 @@ def latent_attention_tc(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor,
     _check(lib().atom_latent_attention_tc(out.data_ptr(), q.data_ptr(), pages.data_ptr(), block_table.data_ptr(),
                                           block_table.shape[1], pages.shape[1], cu_q.data_ptr(), positions.data_ptr(),
                                           num_seqs, T, H, kv_rank, rot_dim, float(scale), int(window), _ptr(sink),
-                                          _stream()), "latent_attention_tc")
+                                          _ptr(scratch), int(nsplit), int(rows), _stream()), "latent_attention_tc")
+    if nsplit > 1:
+        assert scratch is not None and scratch.dtype == torch.float32 and seq_of_token is not None
+        assert scratch.numel() >= latent_attention_scratch_elems(T, H, kv_rank, nsplit)
+        _check(lib().atom_latent_merge(out.data_ptr(), scratch.data_ptr(), dtype_code(out.dtype), seq_of_token.data_ptr(),
+                                       T, H, kv_rank, int(nsplit), _ptr(sink), _stream()), "latent_merge")
 
 
 def causal_conv(u: torch.Tensor, x: torch.Tensor, bx: torch.Tensor, w: torch.Tensor, bc: torch.Tensor,

@@ -235,15 +235,52 @@ latent_attention_kernel(T* __restrict__ out, float* __restrict__ scratch, const 
   }
 }
 
+constexpr int kLatMergeShares = 64;   // shares whose weights the merge kernel keeps in shared memory
+
 template <typename T>
 __global__ void latent_merge_kernel(T* __restrict__ out, const float* __restrict__ scratch,
                                     const int* __restrict__ seq_of_token, int H, int R, int nsplit,
                                     const float* __restrict__ sink) {
   atom::pdl_trigger();
   atom::pdl_wait();
+  __shared__ float ws[kLatMergeShares];
   const int t = blockIdx.x, h = blockIdx.y;
   if (seq_of_token[t] < 0) return;
   const float* src = scratch + ((int64_t)t * H + h) * nsplit * (R + 2);
+  if (nsplit <= kLatMergeShares) {
+    // warp 0: every share's weight exp(m_z - top) / denominator, once; then each thread sums its columns
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      float m[kLatMergeShares / 32], l[kLatMergeShares / 32];
+      float top = sink ? sink[h] : -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kLatMergeShares / 32; ++i) {
+        const int z = lane + 32 * i;
+        m[i] = z < nsplit ? src[z * (R + 2) + R] : -INFINITY;
+        l[i] = z < nsplit ? src[z * (R + 2) + R + 1] : 0.f;
+        top = fmaxf(top, m[i]);
+      }
+      top = warp_max(top);
+      float den = 0.f;
+#pragma unroll
+      for (int i = 0; i < kLatMergeShares / 32; ++i) {
+        m[i] = (m[i] == -INFINITY) ? 0.f : expf(m[i] - top);
+        den = fmaf(l[i], m[i], den);
+      }
+      den = warp_sum(den) + (sink ? expf(sink[h] - top) : 0.f);
+#pragma unroll
+      for (int i = 0; i < kLatMergeShares / 32; ++i)
+        if (lane + 32 * i < nsplit) ws[lane + 32 * i] = m[i] / den;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < R; d += blockDim.x) {
+      float v = 0.f;
+#pragma unroll 8
+      for (int z = 0; z < nsplit; ++z) v = fmaf(src[z * (R + 2) + d], ws[z], v);
+      out[((int64_t)t * H + h) * R + d] = from_float<T>(v);
+    }
+    return;
+  }
   float top = sink ? sink[h] : -INFINITY;
   for (int z = 0; z < nsplit; ++z) top = fmaxf(top, src[z * (R + 2) + R]);
   float den = sink ? expf(sink[h] - top) : 0.f;
@@ -332,6 +369,23 @@ ATOM_EXPORT int atom_latent_attention_supports(int H, int R, int rd) {
   return hg >= 1 && atom::latent_smem(hg, R, rd) <= 200 * 1024;
 }
 
+// out[t, h, :] from the shares' partial sums in scratch [T, H, nsplit, R + 2] (either attention kernel leaves them).
+ATOM_EXPORT int atom_latent_merge(void* out, const float* scratch, int dtype, const int* seq_of_token, int T, int H,
+                                  int R, int nsplit, const float* sink, cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (H <= 0 || H > 65535 || R <= 0 || nsplit < 1 || !scratch) return ATOM_ERR_ARG;
+  const int threads = R >= 256 ? 256 : 64;
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::latent_merge_kernel<float>, dim3(T, H), dim3(threads), 0, stream, (float*)out, scratch,
+                     seq_of_token, H, R, nsplit, sink);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::latent_merge_kernel<__nv_bfloat16>, dim3(T, H), dim3(threads), 0, stream,
+                     (__nv_bfloat16*)out, scratch, seq_of_token, H, R, nsplit, sink);
+  else
+    return ATOM_ERR_ARG;
+  return atom::check_launch();
+}
+
 ATOM_EXPORT int atom_latent_attention(void* out, float* scratch, const float* q, const void* pages, int dtype,
                                       const int* block_table, int table_width, int page_size, const int* positions,
                                       const int* seq_of_token, int T, int H, int R, int rd, float scale, int window,
@@ -362,15 +416,6 @@ ATOM_EXPORT int atom_latent_attention(void* out, float* scratch, const float* q,
     return ATOM_ERR_ARG;
   }
   if (atom::check_launch() != ATOM_OK) return ATOM_ERR_LAUNCH;
-  if (nsplit > 1) {
-    const int threads = R >= 256 ? 256 : 64;
-    if (dtype == ATOM_F32)
-      atom::launch_pdl(atom::latent_merge_kernel<float>, dim3(T, H), dim3(threads), 0, stream, (float*)out, scratch,
-                       seq_of_token, H, R, nsplit, sink);
-    else
-      atom::launch_pdl(atom::latent_merge_kernel<__nv_bfloat16>, dim3(T, H), dim3(threads), 0, stream,
-                       (__nv_bfloat16*)out, scratch, seq_of_token, H, R, nsplit, sink);
-    return atom::check_launch();
-  }
+  if (nsplit > 1) return atom_latent_merge(out, scratch, dtype, seq_of_token, T, H, R, nsplit, sink, stream);
   return ATOM_OK;
 }

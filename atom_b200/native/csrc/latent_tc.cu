@@ -1,7 +1,7 @@
 // Attention over a cached latent on the tensor cores (bfloat16; see latent.cu for the mechanism and the plain
 // kernel).  Because every head reads the same row [c | kr] per key, the heads of a token are rows of one
-// product: a CTA owns 64 query rows = a few consecutive tokens of one request x a group of heads, and walks the
-// keys its tokens may see in tiles of 32:
+// product: a CTA owns 64 query rows = a few consecutive tokens of one request x a group of heads (16 rows in
+// steps of single tokens), and walks the keys its tokens may see, or its share of them, in tiles of 32:
 //   1. the tile's rows come into shared memory once (cp.async, two buffers): they are the K operand of the
 //      scores AND, in their first R columns, the V operand of the output;
 //   2. S[64 x 32] = Q K^T on mma.sync m16n8k16 (each warp two 16 x 8 tiles over all R + rd columns), 32-bit
@@ -9,13 +9,12 @@
 //   3. warp w owns rows 8w .. 8w + 7: scale, window and causal mask, running maximum and sum per row in 32-bit,
 //      the weights written back as two bfloat16 numbers p = hi + lo (16 bits of mantissa);
 //   4. O[64 x R] = O * corr + (P_hi + P_lo) V: warp w owns R / 8 columns of all 64 rows in registers.
-// The learned sink enters the denominator at the end.  Tiles are found from cu_q on the device, so the launch
-// depends on the step's shape alone.
+// The learned sink enters the denominator at the end, or in the merge kernel when the keys were shared out.
+// Tiles are found from cu_q on the device, so the launch depends on the step's shape alone.
 #include "common.cuh"
 
 namespace atom {
 
-constexpr int kTcRows = 64;
 constexpr int kTcKT = 32;
 constexpr int kTcThreads = 256;
 constexpr int kTcSStride = kTcKT + 1;      // floats
@@ -46,23 +45,28 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
-// NT: tiles of 8 value columns per warp; R = 64 * NT.
-template <int NT>
-__global__ void __launch_bounds__(kTcThreads, 1)
+// NT: tiles of 8 value columns per warp; R = 64 * NT.  MI: tiles of 16 query rows per CTA, 4 for steps with prompt
+// portions; 1 for steps of single tokens, where a CTA's rows are one token's heads: the warps then share out the
+// columns of Q and K of one row tile (kTcSlices partial scores that the softmax adds), and two CTAs fit an SM.
+template <int NT, int MI>
+__global__ void __launch_bounds__(kTcThreads, MI == 1 ? 2 : 1)
 latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q,
                            const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
                            int page_size, const int* __restrict__ cu_q, const int* __restrict__ positions, int num_seqs,
-                           int H, int HG, int TT, int rd, float scale, int window, const float* __restrict__ sink) {
+                           int H, int HG, int TT, int rd, float scale, int window, const float* __restrict__ sink,
+                           float* __restrict__ scratch, int nsplit) {
   atom::pdl_trigger();
   constexpr int R = 64 * NT;
+  constexpr int kTcRows = 16 * MI;
+  constexpr int kSlices = MI == 1 ? 4 : 1;
   const int Dk = R + rd, Dp = Dk + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [64][Dp]
   __nv_bfloat16* Ks = Qs + kTcRows * Dp;                                          // [2][32][Dp]
   __nv_bfloat16* Ph = Ks + 2 * kTcKT * Dp;                                        // [64][40]
   __nv_bfloat16* Pl = Ph + kTcRows * kTcPStride;                                  // [64][40]
-  float* Ss = reinterpret_cast<float*>(Pl + kTcRows * kTcPStride);                // [64][33]
-  float* ms = Ss + kTcRows * kTcSStride;                                          // [64]
+  float* Ss = reinterpret_cast<float*>(Pl + kTcRows * kTcPStride);                // [slices][rows][33]
+  float* ms = Ss + kSlices * kTcRows * kTcSStride;                                // [rows]
   float* ls = ms + kTcRows;
   float* cs = ls + kTcRows;
 
@@ -72,6 +76,7 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
     const int a = cu_q[s], n = cu_q[s + 1] - a;
     const int tiles = (n + TT - 1) / TT;
     if (idx < tiles) {
+      idx = tiles - 1 - idx;      // a request's last tiles see the most keys: they start first
       tok0 = a + idx * TT;
       ntok = min(TT, n - idx * TT);
       break;
@@ -86,6 +91,13 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
   const int k_lo = window > 0 ? max(0, p0 - window + 1) : 0;
   const int k_hi = p0 + ntok - 1;
   const int n_tiles = (k_hi - k_lo + kTcKT) / kTcKT;
+  // with nsplit > 1 this CTA walks one share of the tiles and leaves unnormalised sums for the merge kernel
+  int tile_begin = 0, tile_end = n_tiles;
+  if (nsplit > 1) {
+    const int per = (n_tiles + nsplit - 1) / nsplit;
+    tile_begin = min(n_tiles, (int)blockIdx.z * per);
+    tile_end = min(n_tiles, tile_begin + per);
+  }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunks_per_row = Dk / 8;
 
@@ -106,41 +118,60 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
     cp_async_commit();
   };
 
-  load_tile(0, 0);
+  if (tile_begin < tile_end) load_tile(tile_begin, 0);
   // queries: 32-bit in, bfloat16 in shared memory; rows without a (token, head) are zeros
-  for (int i = tid; i < kTcRows * Dk; i += kTcThreads) {
-    const int r = i / Dk, d = i - r * Dk;
+  const int q4 = Dk / 4;
+  for (int i = tid; i < kTcRows * q4; i += kTcThreads) {
+    const int r = i / q4, d = (i - r * q4) * 4;
     const int ti = r / HG, hi = r - ti * HG;
-    float v = 0.f;
-    if (ti < ntok && hi < hg) v = q[((int64_t)(tok0 + ti) * H + h0 + hi) * Dk + d];
-    Qs[r * Dp + d] = __float2bfloat16_rn(v);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ti < ntok && hi < hg) v = *reinterpret_cast<const float4*>(q + ((int64_t)(tok0 + ti) * H + h0 + hi) * Dk + d);
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(Qs + r * Dp + d);
+    dst[0] = __floats2bfloat162_rn(v.x, v.y);
+    dst[1] = __floats2bfloat162_rn(v.z, v.w);
   }
   for (int i = tid; i < kTcRows; i += kTcThreads) {
     ms[i] = -INFINITY;
     ls[i] = 0.f;
   }
-  float acc[4][NT][4];
+  float acc[MI][NT][4];
 #pragma unroll
-  for (int mi = 0; mi < 4; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[mi][nt][e] = 0.f;
 
   const int g = lane >> 2, t4 = lane & 3;
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int buf = tile & 1;
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int buf = (tile - tile_begin) & 1;
     cp_async_wait_all();
     __syncthreads();                                    // tile's rows (and, the first time, Q) are in place
-    if (tile + 1 < n_tiles) load_tile(tile + 1, buf ^ 1);
+    if (tile + 1 < tile_end) load_tile(tile + 1, buf ^ 1);
     const __nv_bfloat16* Kt = Ks + buf * kTcKT * Dp;
     const int k0 = k_lo + tile * kTcKT;
-    {   // scores: this warp's 16 rows x 16 keys
-      const int mi = warp >> 1, nb = (warp & 1) * 16;
+    {   // scores: this warp's 16 rows x 16 keys (over its slice of the columns)
+      const int mi = MI == 1 ? 0 : warp >> 1, nb = (warp & 1) * 16;
+      const int slice = MI == 1 ? warp >> 1 : 0;
+      const int steps = Dk / 16, per_slice = (steps + kSlices - 1) / kSlices;
+      const int k_end = min(steps, (slice + 1) * per_slice) * 16;
       float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float sd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};     // odd steps: four sums in flight, not two
       const __nv_bfloat16* ap = Qs + (mi * 16 + (lane & 15)) * Dp + (lane >> 4) * 8;
       const __nv_bfloat16* bp = Kt + (nb + (lane & 7) + ((lane >> 4) << 3)) * Dp + ((lane >> 3) & 1) * 8;
-      for (int kk = 0; kk < Dk; kk += 16) {
+      int kk = slice * per_slice * 16;
+      for (; kk + 32 <= k_end; kk += 32) {
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
+        ldsm_x4(a0, a1, a2, a3, ap + kk);
+        ldsm_x4(b0, b1, b2, b3, bp + kk);
+        ldsm_x4(c0, c1, c2, c3, ap + kk + 16);
+        ldsm_x4(d0, d1, d2, d3, bp + kk + 16);
+        mma_bf16(sc[0], a0, a1, a2, a3, b0, b1);
+        mma_bf16(sc[1], a0, a1, a2, a3, b2, b3);
+        mma_bf16(sd[0], c0, c1, c2, c3, d0, d1);
+        mma_bf16(sd[1], c0, c1, c2, c3, d2, d3);
+      }
+      if (kk < k_end) {
         uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
         ldsm_x4(a0, a1, a2, a3, ap + kk);
         ldsm_x4(b0, b1, b2, b3, bp + kk);
@@ -148,8 +179,12 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
         mma_bf16(sc[1], a0, a1, a2, a3, b2, b3);
       }
 #pragma unroll
+      for (int n2 = 0; n2 < 2; ++n2)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[n2][e] += sd[n2][e];
+#pragma unroll
       for (int n2 = 0; n2 < 2; ++n2) {
-        float* d0 = Ss + (mi * 16 + g) * kTcSStride + nb + n2 * 8 + 2 * t4;
+        float* d0 = Ss + (slice * kTcRows + mi * 16 + g) * kTcSStride + nb + n2 * 8 + 2 * t4;
         d0[0] = sc[n2][0];
         d0[1] = sc[n2][1];
         d0[8 * kTcSStride] = sc[n2][2];
@@ -157,15 +192,18 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
       }
     }
     __syncthreads();
-    {   // softmax: warp w owns rows 8w .. 8w + 7, a lane is a key
+    {   // softmax: warp w owns rows 2 MI w .. 2 MI (w + 1) - 1, a lane is a key
       const int key = k0 + lane;
 #pragma unroll
-      for (int rr = 0; rr < 8; ++rr) {
-        const int r = warp * 8 + rr;
+      for (int rr = 0; rr < 2 * MI; ++rr) {
+        const int r = warp * 2 * MI + rr;
         const int ti = r / HG;
         const int p = p0 + ti;
         const bool seen = ti < ntok && key <= p && key <= k_hi && (window <= 0 || p - key < window);
-        const float sc = seen ? Ss[r * kTcSStride + lane] * scale : -INFINITY;
+        float raw = Ss[r * kTcSStride + lane];
+#pragma unroll
+        for (int sl = 1; sl < kSlices; ++sl) raw += Ss[(sl * kTcRows + r) * kTcSStride + lane];
+        const float sc = seen ? raw * scale : -INFINITY;
         const float m_old = ms[r];
         const float m_new = fmaxf(m_old, warp_max(sc));
         const float pw = (sc == -INFINITY) ? 0.f : expf(sc - m_new);
@@ -183,15 +221,15 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
       }
     }
     __syncthreads();
-    {   // output: this warp's R / 8 columns of all 64 rows
-      float c[4][2];
+    {   // output: this warp's R / 8 columns of all rows
+      float c[MI][2];
 #pragma unroll
-      for (int mi = 0; mi < 4; ++mi) {
+      for (int mi = 0; mi < MI; ++mi) {
         c[mi][0] = cs[mi * 16 + g];
         c[mi][1] = cs[mi * 16 + g + 8];
       }
 #pragma unroll
-      for (int mi = 0; mi < 4; ++mi)
+      for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           acc[mi][nt][0] *= c[mi][0];
@@ -202,9 +240,9 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
       const int colbase = warp * 8 * NT;
 #pragma unroll
       for (int ks = 0; ks < kTcKT / 16; ++ks) {
-        uint32_t ah[4][4], al[4][4];
+        uint32_t ah[MI][4], al[MI][4];
 #pragma unroll
-        for (int mi = 0; mi < 4; ++mi) {
+        for (int mi = 0; mi < MI; ++mi) {
           const int off = (mi * 16 + (lane & 15)) * kTcPStride + ks * 16 + (lane >> 4) * 8;
           ldsm_x4(ah[mi][0], ah[mi][1], ah[mi][2], ah[mi][3], Ph + off);
           ldsm_x4(al[mi][0], al[mi][1], al[mi][2], al[mi][3], Pl + off);
@@ -214,7 +252,7 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
           uint32_t b0, b1;
           ldsm_x2_trans(b0, b1, Kt + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * Dp + colbase + nt * 8);
 #pragma unroll
-          for (int mi = 0; mi < 4; ++mi) {
+          for (int mi = 0; mi < MI; ++mi) {
             mma_bf16(acc[mi][nt], ah[mi][0], ah[mi][1], ah[mi][2], ah[mi][3], b0, b1);
             mma_bf16(acc[mi][nt], al[mi][0], al[mi][1], al[mi][2], al[mi][3], b0, b1);
           }
@@ -225,12 +263,24 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
   __syncthreads();
   // the sink joins the denominator; rows that are a (token, head) go out
 #pragma unroll
-  for (int mi = 0; mi < 4; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int r = mi * 16 + g + half * 8;
       const int ti = r / HG, hi = r - ti * HG;
       if (ti >= ntok || hi >= hg) continue;
+      if (nsplit > 1) {
+        float* dst = scratch + (((int64_t)(tok0 + ti) * H + h0 + hi) * nsplit + blockIdx.z) * (R + 2);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          *reinterpret_cast<float2*>(dst + warp * 8 * NT + nt * 8 + 2 * t4) =
+              make_float2(acc[mi][nt][half * 2], acc[mi][nt][half * 2 + 1]);
+        if (warp == 0 && t4 == 0) {
+          dst[R] = ms[r];
+          dst[R + 1] = ls[r];
+        }
+        continue;
+      }
       const float m = ms[r], sk = sink ? sink[h0 + hi] : -INFINITY;
       const float top = fmaxf(m, sk);
       const float w = expf(m - top);
@@ -244,24 +294,26 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
     }
 }
 
-static inline size_t latent_tc_smem(int R, int rd) {
-  const int Dp = R + rd + 8;
-  return sizeof(__nv_bfloat16) * ((size_t)kTcRows * Dp + 2 * (size_t)kTcKT * Dp + 2 * (size_t)kTcRows * kTcPStride) +
-         sizeof(float) * ((size_t)kTcRows * kTcSStride + 3 * kTcRows);
+static inline size_t latent_tc_smem(int R, int rd, int rows) {
+  const int Dp = R + rd + 8, slices = rows == 16 ? 4 : 1;
+  return sizeof(__nv_bfloat16) * ((size_t)rows * Dp + 2 * (size_t)kTcKT * Dp + 2 * (size_t)rows * kTcPStride) +
+         sizeof(float) * ((size_t)slices * rows * kTcSStride + 3 * rows);
 }
 
-template <int NT>
+template <int NT, int MI>
 static int launch_latent_tc(__nv_bfloat16* out, const float* q, const __nv_bfloat16* pages, const int* block_table,
                             int table_width, int page_size, const int* cu_q, const int* positions, int num_seqs, int T,
-                            int H, int rd, float scale, int window, const float* sink, cudaStream_t stream) {
+                            int H, int rd, float scale, int window, const float* sink, float* scratch, int nsplit,
+                            cudaStream_t stream) {
+  constexpr int kTcRows = 16 * MI;
   const int HG = H < kTcRows ? H : kTcRows;
   const int TT = kTcRows / HG;
-  const size_t smem = latent_tc_smem(64 * NT, rd);
-  auto k = latent_attention_tc_kernel<NT>;
+  const size_t smem = latent_tc_smem(64 * NT, rd, kTcRows);
+  auto k = latent_attention_tc_kernel<NT, MI>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ATOM_ERR_LAUNCH;
-  const dim3 grid((T + TT - 1) / TT + num_seqs, (H + HG - 1) / HG);
+  const dim3 grid((T + TT - 1) / TT + num_seqs, (H + HG - 1) / HG, nsplit);
   launch_pdl(k, grid, dim3(kTcThreads), smem, stream, out, q, pages, block_table, table_width, page_size, cu_q, positions,
-             num_seqs, H, HG, TT, rd, scale, window, sink);
+             num_seqs, H, HG, TT, rd, scale, window, sink, scratch, nsplit);
   return check_launch();
 }
 
@@ -270,23 +322,33 @@ static int launch_latent_tc(__nv_bfloat16* out, const float* q, const __nv_bfloa
 ATOM_EXPORT int atom_latent_attention_tc_supports(int H, int R, int rd) {
   if (H <= 0 || rd < 0 || rd % 16) return 0;
   if (R != 64 && R != 128 && R != 256 && R != 512) return 0;
-  return atom::latent_tc_smem(R, rd) <= 220 * 1024;
+  return atom::latent_tc_smem(R, rd, 64) <= 220 * 1024;
 }
 
-// out: [T, H, R] bfloat16; q: [T, H, R + rd] float; pages: [pages, page, R + rd] bfloat16.
+// out: [T, H, R] bfloat16; q: [T, H, R + rd] float; pages: [pages, page, R + rd] bfloat16.  rows: 64 query rows per
+// CTA (steps with prompt portions) or 16 (steps of single tokens).  nsplit > 1: partial sums to scratch
+// [T, H, nsplit, R + 2], to be put together by atom_latent_merge.
 ATOM_EXPORT int atom_latent_attention_tc(void* out, const float* q, const void* pages, const int* block_table,
                                          int table_width, int page_size, const int* cu_q, const int* positions,
                                          int num_seqs, int T, int H, int R, int rd, float scale, int window,
-                                         const float* sink, cudaStream_t stream) {
+                                         const float* sink, float* scratch, int nsplit, int rows, cudaStream_t stream) {
   if (T <= 0 || num_seqs <= 0) return ATOM_OK;
-  if (!atom_latent_attention_tc_supports(H, R, rd) || page_size <= 0 || window < 0) return ATOM_ERR_ARG;
+  if (!atom_latent_attention_tc_supports(H, R, rd) || page_size <= 0 || window < 0 || nsplit < 1 || nsplit > 65535 ||
+      (nsplit > 1 && !scratch) || (rows != 16 && rows != 64))
+    return ATOM_ERR_ARG;
   auto* o = (__nv_bfloat16*)out;
   auto* pg = (const __nv_bfloat16*)pages;
+#define ATOM_LATENT_TC(NT)                                                                                            \
+  return rows == 16 ? atom::launch_latent_tc<NT, 1>(o, q, pg, block_table, table_width, page_size, cu_q, positions,   \
+                                                    num_seqs, T, H, rd, scale, window, sink, scratch, nsplit, stream) \
+                    : atom::launch_latent_tc<NT, 4>(o, q, pg, block_table, table_width, page_size, cu_q, positions,   \
+                                                    num_seqs, T, H, rd, scale, window, sink, scratch, nsplit, stream)
   switch (R) {
-    case 64: return atom::launch_latent_tc<1>(o, q, pg, block_table, table_width, page_size, cu_q, positions, num_seqs, T, H, rd, scale, window, sink, stream);
-    case 128: return atom::launch_latent_tc<2>(o, q, pg, block_table, table_width, page_size, cu_q, positions, num_seqs, T, H, rd, scale, window, sink, stream);
-    case 256: return atom::launch_latent_tc<4>(o, q, pg, block_table, table_width, page_size, cu_q, positions, num_seqs, T, H, rd, scale, window, sink, stream);
-    case 512: return atom::launch_latent_tc<8>(o, q, pg, block_table, table_width, page_size, cu_q, positions, num_seqs, T, H, rd, scale, window, sink, stream);
+    case 64: ATOM_LATENT_TC(1);
+    case 128: ATOM_LATENT_TC(2);
+    case 256: ATOM_LATENT_TC(4);
+    case 512: ATOM_LATENT_TC(8);
   }
+#undef ATOM_LATENT_TC
   return ATOM_ERR_ARG;
 }

@@ -31,9 +31,6 @@ from .registry import register
 from .spec import CacheEntry, CacheNeed, ParamSpec, PartSpec
 
 
-TC_MIN_TOKENS = 32     # steps with a portion and at least this many tokens run on the tensor-core kernel
-
-
 @register("mixer", "latent_attention")
 class LatentAttention(Mixer):
     graph_safe = True
@@ -92,18 +89,23 @@ class LatentAttention(Mixer):
         self._freq = self.position.frequencies(self.rt)
 
     def launch_plan(self, step):
-        """(whether the tensor-core kernel runs, into how many shares the plain kernel cuts every token's keys).  The
-        tensor-core kernel's CTA is a few consecutive tokens of a request, so it pays in steps with prompt portions;
-        in a step of single tokens the plain kernel, a CTA per token and group of heads, shares out the keys."""
+        """(query rows of a tensor-core tile, or 0 for the plain kernel; into how many shares every unit's keys are
+        cut).  The tensor-core kernel's unit is a tile of a few consecutive tokens of a request with a group of heads:
+        64 rows in steps with prompt portions, 16 in steps of single tokens; the plain kernel's is a token with a group
+        of heads.  Where the units do not fill the device (decoding, short portions) their keys are shared out."""
         key = ("latent_attention", self.nh, self.R, self.rd, self.window or 0)
         plan = step.plans.get(key)
         if plan is None:
             longest = min(step.max_ctx_len, self.window) if self.window else step.max_ctx_len
-            tc = (native.LATENT_TC and step.max_q_len > 1 and step.num_tokens >= TC_MIN_TOKENS
-                  and native.latent_attention_tc_supports(self.nh, self.R, self.rd, self.rt.dtype))
-            groups = -(-self.nh // native.latent_attention_head_group(self.nh, self.R, self.rd))
-            plan = step.plans[key] = (tc, 1 if tc else native.attention_mixed_splits(step.num_tokens * groups, longest,
-                                                                                     per_sm=2, min_share=64))
+            if native.LATENT_TC and native.latent_attention_tc_supports(self.nh, self.R, self.rd, self.rt.dtype):
+                rows = 16 if step.max_q_len <= 1 else 64
+                per_tile = native.latent_attention_tc_tile_tokens(self.nh, rows)
+                tiles = step.num_tokens if step.max_q_len <= 1 else -(-step.num_tokens // per_tile) + step.num_seqs - 1
+                units, per_sm, share = tiles * -(-self.nh // rows), (2 if rows == 16 else 1), (32 if rows == 16 else 64)
+            else:
+                rows, per_sm, share = 0, 2, 64
+                units = step.num_tokens * -(-self.nh // native.latent_attention_head_group(self.nh, self.R, self.rd))
+            plan = step.plans[key] = (rows, native.attention_mixed_splits(units, longest, per_sm=per_sm, min_share=share))
         return plan
 
     def forward(self, x, step, cache, writes_cache):
@@ -129,14 +131,14 @@ class LatentAttention(Mixer):
         native.rotate_pairs(qf, R, q, dn, rd, pos.rotary_dim, self._freq, pos.magnitude, step.positions,
                             step.seq_of_token)
         olat = ws.get("lat.olat", (T, H, R), dt)
-        tc, nsplit = self.launch_plan(step)
-        if tc:
+        tile_rows, nsplit = self.launch_plan(step)
+        scratch = None
+        if nsplit > 1:
+            scratch = ws.get("lat.splits", (native.latent_attention_scratch_elems(T, H, R, nsplit),), torch.float32)
+        if tile_rows:
             native.latent_attention_tc(olat, qf, pages, bt, step.positions, step.cu_q, step.num_seqs, R, rd, self.scale,
-                                       self.window or 0, self._sink)
+                                       self.window or 0, self._sink, nsplit, scratch, step.seq_of_token, tile_rows)
         else:
-            scratch = None
-            if nsplit > 1:
-                scratch = ws.get("lat.splits", (native.latent_attention_scratch_elems(T, H, R, nsplit),), torch.float32)
             native.latent_attention(olat, qf, pages, bt, step.positions, step.seq_of_token, R, rd, self.scale,
                                     self.window or 0, self._sink, nsplit, scratch)
         heads = ws.get("lat.heads", (T, H, dv), dt)

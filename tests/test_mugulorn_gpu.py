@@ -121,9 +121,10 @@ def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0
         ns = nsplit or native.attention_mixed_splits(n, min(at + n, window) if window else at + n)
         scratch = torch.empty(native.latent_attention_scratch_elems(n, H, R, ns), dtype=torch.float32, device=DEV) if ns > 1 else None
         o = torch.zeros(n, H, R, dtype=dt, device=DEV)
-        if kernel == "tc":
+        if kernel.startswith("tc"):
             native.latent_attention_tc(o, q[at:at + n].float().contiguous().to(DEV), cache.pages, cache.table,
-                                       _i32(range(at, at + n)), _i32([0, n]), 1, R, rd, scale, window, sk)
+                                       _i32(range(at, at + n)), _i32([0, n]), 1, R, rd, scale, window, sk,
+                                       ns, scratch, _i32([0] * n), rows=int(kernel[2:]))
         else:
             native.latent_attention(o, q[at:at + n].float().contiguous().to(DEV), cache.pages, cache.table,
                                     _i32(range(at, at + n)), _i32([0] * n), R, rd, scale, window, sk, ns, scratch)
@@ -141,9 +142,10 @@ LATENT_CASES = [  # H, R, rd, window, page, T
 
 
 def _kernels(H, R, rd, dtype):
-    """The kernels that take these sizes: the plain one always, the tensor-core one where it does."""
+    """The kernels that take these sizes: the plain one always, the tensor-core one (tiles of 64 and of 16 query rows) where
+    it does."""
     from atom_b200 import native
-    return ["plain", "tc"] if native.latent_attention_tc_supports(H, R, rd, _dt(dtype)) else ["plain"]
+    return ["plain", "tc64", "tc16"] if native.latent_attention_tc_supports(H, R, rd, _dt(dtype)) else ["plain"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -165,16 +167,16 @@ def test_latent_attention_in_prompts_portions_and_decoding(case, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nsplit", [2, 3, 7, 40])
 def test_latent_attention_with_keys_shared_out_among_blocks(nsplit, dtype):
-    H, R, rd, window, page, T = 4, 32, 8, 0, 16, 333
+    H, R, rd, window, page, T = 4, 64, 16, 0, 16, 333
     g = torch.Generator().manual_seed(nsplit)
     q = torch.randn(T, H, R + rd, generator=g).double()
     rows = _rounded(torch.randn(T, R + rd, generator=g), dtype)
     sink = torch.randn(H, generator=g).double()
-    want = _plain_latent_scores(q.float().double(), rows, R, 0.3, window, sink)
-    for w in (0, 50):
-        want = _plain_latent_scores(q.float().double(), rows, R, 0.3, w, sink)
-        got = _run_latent(q, rows, R, rd, 0.3, w, sink, dtype, page, [T - 5, 1, 1, 1, 1, 1], nsplit=nsplit)
-        _close(got, want, dtype, f"window {w}", f32=2e-5, bf16=1e-2)
+    for kernel in _kernels(H, R, rd, dtype):
+        for w in (0, 50):
+            want = _plain_latent_scores(q.float().double(), rows, R, 0.3, w, sink)
+            got = _run_latent(q, rows, R, rd, 0.3, w, sink, dtype, page, [T - 5, 1, 1, 1, 1, 1], nsplit=nsplit, kernel=kernel)
+            _close(got, want, dtype, f"{kernel}, window {w}", f32=2e-5, bf16=1e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -203,7 +205,7 @@ def test_one_key_at_the_windows_edge_stands_out(window, dtype):
     for cuts in ([T], [edge - 1, 1, 1, 1, T], [edge, T], [edge + 1, T], [needle + 1] + [1] * (T - needle - 1) if window <= 64 else [T],
                  [needle, 2, window, 2, T]):
         for kernel in _kernels(H, R, rd, dtype):
-            if kernel == "tc" and len(cuts) > 20:
+            if kernel == "tc64" and len(cuts) > 20:
                 continue
             got = _run_latent(q, rows, R, rd, 1.0, window, sink, dtype, page, cuts, kernel=kernel)
             what = f"{kernel}, window {window}, cuts {cuts[:4]}"
