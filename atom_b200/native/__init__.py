@@ -200,6 +200,8 @@ def _cuda(*tensors) -> None:
 
 # --------------------------------------------------------------------------- wrappers
 
+GATE_ACTS = {"silu": 1, "gelu_tanh": 2}      # the activation on the gate of a gated product (gemm_rows, gemm_pairs)
+
 
 def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
     """out[t] = table[ids[t]] * scale widened to float32.  out [T,H] f32, table [V,H], ids [T] i32."""
@@ -819,9 +821,10 @@ def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
               bias: Optional[torch.Tensor] = None, gated: bool = False, ssq_in: Optional[torch.Tensor] = None,
               norm_size: int = 0, norm_eps: float = 0.0, residual: Optional[torch.Tensor] = None,
               norm_w: Optional[torch.Tensor] = None, xout: Optional[torch.Tensor] = None,
-              ssq_out: Optional[torch.Tensor] = None) -> None:
+              ssq_out: Optional[torch.Tensor] = None, act: str = "silu") -> None:
     """out[M, N] = x[M, K] w[N, K]^T for at most 16 rows of bf16 x, with one of the epilogues of
-    csrc/gemm_rows.h: plain (+ bias; out bf16 or float32); ``gated`` (w = [gate ; up] of 2N rows);
+    csrc/gemm_rows.h: plain (+ bias; out bf16 or float32); ``gated`` (w = [gate ; up] of 2N rows, ``act`` "silu" or
+    "gelu_tanh" on the gate);
     ``residual`` (float32 [M, N], += product in place, with ``xout`` = bf16(residual * norm_w) and the CTAs'
     sums of squares in ``ssq_out`` [gemm_rows_grid(), 16]).  ``ssq_in`` (such sums, of ``norm_size`` columns):
     every output row is first multiplied by its rstd."""
@@ -846,7 +849,7 @@ def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     c.out_dtype = dtype_code(out.dtype) if out is not None else BF16
     c.ldc = out.stride(0) if out is not None else 0
     c.bias, c.bias_dtype = _ptr(bias), (dtype_code(bias.dtype) if bias is not None else F32)
-    c.N, c.K, c.gated = N, K, int(gated)
+    c.N, c.K, c.gated = N, K, (GATE_ACTS[act] if gated else 0)
     c.ssq_in = _ptr(ssq_in)
     c.ssq_parts = ssq_in.numel() // 16 if ssq_in is not None else 0
     c.norm_size, c.norm_eps = int(norm_size), float(norm_eps)
@@ -884,16 +887,16 @@ def gemm_pairs_waves(M: int, N: int, gated: bool) -> float:
     return tiles / (waves * pairs)
 
 
-def gemm_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+def gemm_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False, act: str = "silu") -> None:
     """out[M, N] = x[M, K] w[N, K]^T in bf16 on tcgen05 with two CTAs to a tile; ``gated``: w = [gate ; up]
-    of 2N rows, out = silu(x gate^T) * (x up^T) (csrc/gemm_pairs.cu)."""
+    of 2N rows, out = act(x gate^T) * (x up^T), ``act`` "silu" or "gelu_tanh" (csrc/gemm_pairs.cu)."""
     M, K = x.shape
     N = out.shape[1]
     _cuda(x, w, out)
     assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and w.shape[1] == K and w.is_contiguous()
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == M and w.shape[0] == (2 * N if gated else N)
     _check(lib().atom_gemm_pairs(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), M, N, K,
-                                 int(gated), error_flag(x.device).data_ptr(), _stream()), "gemm_pairs")
+                                 GATE_ACTS[act] if gated else 0, error_flag(x.device).data_ptr(), _stream()), "gemm_pairs")
 
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:

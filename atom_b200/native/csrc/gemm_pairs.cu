@@ -1,7 +1,7 @@
 // Matrix product for many rows on the 5th-generation tensor cores, two CTAs to a tile (tcgen05 with
 // cta_group::2), bf16 in, 32-bit sums in tensor memory, bf16 out:
 //     plain:   C[M, N] = X[M, K] W[N, K]^T
-//     gated:   W = [gate ; up] of N rows each, C[M, N] = silu(X gate^T) * (X up^T)
+//     gated:   W = [gate ; up] of N rows each, C[M, N] = act(X gate^T) * (X up^T), act = silu or gelu_tanh
 // It is the prefill feed-forward's first product with the activation in its epilogue: the sums never
 // leave the chip, and the activation kernel with its pass over [M, 2N] goes away.
 //
@@ -53,6 +53,7 @@ struct Params {
   int mt, nt;         // tiles of 256 rows, tiles of 512 columns of sums
   int full_items;     // work items [0, full_items) are whole tiles, the others halves of the tiles that follow
   int items;
+  int act;            // gated: 1 silu, 2 gelu_tanh
   int* error;
 };
 
@@ -171,6 +172,12 @@ __device__ __forceinline__ float silu(float x) {
   float t;
   asm("tanh.approx.f32 %0, %1;\n" : "=f"(t) : "f"(0.5f * x));
   return x * (0.5f + 0.5f * t);
+}
+
+// z/2 (1 + tanh(a)) = z / (1 + exp(-2a)), a = sqrt(2/pi) (z + 0.044715 z^3).
+__device__ __forceinline__ float gelu_tanh(float z) {
+  const float a = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return __fdividef(z, 1.f + __expf(fminf(-2.f * a, 80.f)));
 }
 
 struct Item {
@@ -341,7 +348,7 @@ gemm_pairs_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constan
             tmem_ld32(tbase + h * 256 + 128 + b * 64 + ch * 32, u);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) g[j] = silu(g[j]) * u[j];
+            for (int j = 0; j < 32; ++j) g[j] = (p.act == 2 ? gelu_tanh(g[j]) : silu(g[j])) * u[j];
             pack(g, o[h][b]);
           }
           tc_fence_before();
@@ -440,7 +447,8 @@ static int plan_items(int tiles, int pairs, int* full_items) {
 ATOM_EXPORT int atom_gemm_pairs(const void* X, int64_t lda, const void* W, void* out, int64_t ldc, int M, int N, int K,
                                 int gated, int* error, cudaStream_t stream) {
   using namespace atom::pairs;
-  if (X == nullptr || W == nullptr || out == nullptr || error == nullptr || !atom_gemm_pairs_supports(M, N, K, lda, ldc) ||
+  if (X == nullptr || W == nullptr || out == nullptr || error == nullptr || gated < 0 || gated > 2 ||
+      !atom_gemm_pairs_supports(M, N, K, lda, ldc) ||
       ((uintptr_t)X % 16) != 0 || ((uintptr_t)W % 16) != 0 || ((uintptr_t)out % 16) != 0)
     return ATOM_ERR_ARG;
   int pairs = resident_pairs();
@@ -455,6 +463,7 @@ ATOM_EXPORT int atom_gemm_pairs(const void* X, int64_t lda, const void* W, void*
   p.K = K;
   p.mt = (M + 255) / 256;
   p.nt = gated ? (N + 255) / 256 : (N + 511) / 512;
+  p.act = gated;
   p.error = error;
   const int tiles = p.mt * p.nt;
   if (pairs > tiles) pairs = tiles;

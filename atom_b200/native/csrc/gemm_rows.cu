@@ -43,6 +43,12 @@ namespace rows {
 
 using namespace atom::tma;
 
+// z/2 (1 + tanh(a)) = z / (1 + exp(-2a)), a = sqrt(2/pi) (z + 0.044715 z^3).
+__device__ __forceinline__ float gelu_tanh(float z) {
+  const float a = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z / (1.f + __expf(fminf(-2.f * a, 80.f)));
+}
+
 __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
                : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
@@ -372,7 +378,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           sq[nt] += rr * rr;
         } else {
           if (gated)
-            sum = sum / (1.f + __expf(-sum)) * (up * scale[nt]);
+            sum = (p.gated == 2 ? gelu_tanh(sum) : sum / (1.f + __expf(-sum))) * (up * scale[nt]);
           else
             sum += bias;
           if (p.out_dtype == ATOM_F32)
@@ -443,7 +449,7 @@ ATOM_EXPORT int atom_gemm_rows(const AtomRowsOp* op, int M, int* error, cudaStre
   if (op == nullptr || error == nullptr) return ATOM_ERR_ARG;
   const AtomRowsOp& a = *op;
   const bool res = a.residual != nullptr;
-  if (!atom_gemm_rows_supports(M, a.N, a.K, a.lda) || (a.gated && a.bias != nullptr) ||
+  if (!atom_gemm_rows_supports(M, a.N, a.K, a.lda) || a.gated < 0 || a.gated > 2 || (a.gated && a.bias != nullptr) ||
       ((uintptr_t)a.X % 16) != 0 || ((uintptr_t)a.W % 16) != 0)
     return ATOM_ERR_ARG;
   if (!res && (a.out == nullptr || a.ldc < a.N || (a.out_dtype != ATOM_F32 && a.out_dtype != ATOM_BF16)))
@@ -482,7 +488,7 @@ ATOM_EXPORT int atom_gemm_rows(const AtomRowsOp* op, int M, int* error, cudaStre
   p.bias_dtype = a.bias_dtype;
   p.N = a.N;
   p.K = a.K;
-  p.gated = a.gated ? 1 : 0;
+  p.gated = a.gated;
   p.ssq_in = a.ssq_in;
   p.ssq_parts = a.ssq_parts;
   p.inv_norm_size = a.norm_size > 0 ? 1.f / (float)a.norm_size : 0.f;

@@ -4,7 +4,7 @@
 
 // One product  C[M, N] = X[M, K] * W[N, K]^T,  X and W bf16, M <= 16, with one of the epilogues
 //   plain:     (+ bias), stored as bf16 or 32-bit into out (leading dimension ldc);
-//   gated:     W is [2N, K] = [gate ; up], out = silu(X gate^T) * (X up^T);
+//   gated:     W is [2N, K] = [gate ; up], out = act(X gate^T) * (X up^T), act = silu (gated 1) or gelu_tanh (2);
 //   residual:  residual[M, N] (32-bit, in place) += product; xout[M, N] = bf16(residual * norm_w);
 //              ssq_out[c * 16 + m] = sum of residual[m, j]^2 over the columns j of CTA c, for every
 //              c < atom_gemm_rows_grid()  (out is unused).

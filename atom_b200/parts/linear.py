@@ -110,21 +110,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
     return out
 
 
-def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scratch) -> torch.Tensor:
-    """out[M, I] = silu(x W_gate^T) * (x W_up^T) for weight [2I, K] = [gate ; up].  Few rows, and
-    long portions in bf16 (``pairs_pay``): one kernel, the activation fused into the product.  Else
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scratch, act: str = "silu") -> torch.Tensor:
+    """out[M, I] = act(x W_gate^T) * (x W_up^T) for weight [2I, K] = [gate ; up], act "silu" or "gelu_tanh".  Few
+    rows, and long portions in bf16 (``pairs_pay``): one kernel, the activation fused into the product.  Else
     the product into ``scratch(M, 2I)`` and the activation kernel."""
     M, K = x.shape
     I = weight.shape[0] // 2
     if isinstance(x, ScaledRows):
-        native.gemm_rows(x.x, weight, out, gated=True, ssq_in=x.ssq, norm_size=x.size, norm_eps=x.eps)
+        native.gemm_rows(x.x, weight, out, gated=True, ssq_in=x.ssq, norm_size=x.size, norm_eps=x.eps, act=act)
         return out
     if x.dtype == torch.bfloat16 and streams(M, I, K, x.stride(0), gated=True):
-        native.gemm_rows(x, weight, out, gated=True)
+        native.gemm_rows(x, weight, out, gated=True, act=act)
         return out
     if x.dtype == torch.bfloat16 and pairs_pay(M, I, K, x.stride(0), out.stride(0)):
-        native.gemm_pairs(x, weight, out, gated=True)
+        native.gemm_pairs(x, weight, out, gated=True, act=act)
         return out
     gu = linear(x, weight, None, scratch(M, 2 * I))
-    native.silu_mul(out, gu)
+    (native.gelu_mul if act == "gelu_tanh" else native.silu_mul)(out, gu)
     return out

@@ -57,9 +57,8 @@ class GatedGeluMLP(FeedForward):
     def forward(self, x, step):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
-        gu = linear(x, self.w_gate_up_weight, None, ws.get("ffn.gate_up", (T, 2 * self.intermediate_size), dt))
-        f = ws.get("ffn.act", (T, self.intermediate_size), dt)
-        native.gelu_mul(f, gu)
+        f = gated_linear(x, self.w_gate_up_weight, ws.get("ffn.act", (T, self.intermediate_size), dt),
+                         lambda m, n: ws.get("ffn.gate_up", (m, n), dt), act="gelu_tanh")
         return linear(f, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))
 
 

@@ -615,16 +615,23 @@ def test_gemm_rows(native, out_dtype, M, N, K):
     torch.testing.assert_close(out.float(), want.to(out_dtype).float(), rtol=1e-2, atol=1e-2 * math.sqrt(K / 96))
 
 
+def _gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+_GATE_ACTS = {"silu": torch.nn.functional.silu, "gelu_tanh": _gelu_tanh}
+
+
 @pytest.mark.parametrize("M,I,K", [(1, 160, 128), (7, 1001, 320), (8, 12288, 4096), (12, 112, 64), (16, 333, 1024),
                                    (3, 5000, 192)])
 def test_gemm_rows_gated(native, M, I, K):
     a, w = _rand((M, K), torch.bfloat16, 33), _rand((2 * I, K), torch.bfloat16, 34, 0.3)
-    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    native.gemm_rows(a, w, out, gated=True)
-    native.check_error_flags()
     gu = a.double() @ w.double().T
-    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
-    torch.testing.assert_close(out.double(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
+    for act, fn in _GATE_ACTS.items():
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        native.gemm_rows(a, w, out, gated=True, act=act)
+        native.check_error_flags()
+        torch.testing.assert_close(out.double(), fn(gu[:, :I]) * gu[:, I:], rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
 
 
 def test_gemm_rows_strided_input_and_output(native):
@@ -675,12 +682,12 @@ def test_gemm_pairs(native, M, N, K):
 def test_gemm_pairs_gated(native, M, I, K):
     """The activation in the epilogue: gate and up sums of an output lie in the same half of a tile."""
     a, w = _rand((M, K), torch.bfloat16, 62), _rand((2 * I, K), torch.bfloat16, 63, 0.3)
-    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    native.gemm_pairs(a, w, out, gated=True)
-    native.check_error_flags()
     gu = a.double() @ w.double().T
-    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
-    torch.testing.assert_close(out.double(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
+    for act, fn in _GATE_ACTS.items():
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        native.gemm_pairs(a, w, out, gated=True, act=act)
+        native.check_error_flags()
+        torch.testing.assert_close(out.double(), fn(gu[:, :I]) * gu[:, I:], rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
 
 
 def test_gemm_pairs_strided_and_batch_independent(native):
