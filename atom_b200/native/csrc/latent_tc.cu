@@ -17,6 +17,7 @@ namespace atom {
 
 constexpr int kTcKT = 32;
 constexpr int kTcThreads = 256;
+static_assert(kTcThreads == 8 * kTcKT, "eight threads copy a key row");
 constexpr int kTcSStride = kTcKT + 1;      // floats
 constexpr int kTcPStride = kTcKT + 8;      // bf16
 
@@ -101,19 +102,18 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunks_per_row = Dk / 8;
 
+  // a tile's row j is copied by threads 8 j .. 8 j + 7 in chunks of 16 bytes: one page lookup per thread and tile
+  const int lrow = tid >> 3, lch = tid & 7;
   auto load_tile = [&](int tile, int buf) {
-    const int k0 = k_lo + tile * kTcKT;
-    __nv_bfloat16* dst = Ks + buf * kTcKT * Dp;
-    for (int c = tid; c < kTcKT * chunks_per_row; c += kTcThreads) {
-      const int j = c / chunks_per_row, ch = c - j * chunks_per_row;
-      const int key = k0 + j;
-      if (key <= k_hi) {
-        const int page = block_table[(int64_t)s * table_width + key / page_size];
-        const __nv_bfloat16* src = pages + ((int64_t)page * page_size + key % page_size) * Dk + ch * 8;
-        cp_async16(dst + j * Dp + ch * 8, src);
-      } else {
-        *reinterpret_cast<uint4*>(dst + j * Dp + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
-      }
+    const int key = k_lo + tile * kTcKT + lrow;
+    __nv_bfloat16* dst = Ks + (buf * kTcKT + lrow) * Dp;
+    if (key <= k_hi) {
+      const int pg = key / page_size;
+      const int page = block_table[(int64_t)s * table_width + pg];
+      const __nv_bfloat16* src = pages + ((int64_t)page * page_size + (key - pg * page_size)) * Dk;
+      for (int ch = lch; ch < chunks_per_row; ch += 8) cp_async16(dst + ch * 8, src + ch * 8);
+    } else {
+      for (int ch = lch; ch < chunks_per_row; ch += 8) *reinterpret_cast<uint4*>(dst + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     cp_async_commit();
   };

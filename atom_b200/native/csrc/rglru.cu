@@ -34,26 +34,50 @@ __device__ __forceinline__ float conv_input(const T* x, int64_t ld, int64_t t, i
 }
 
 // x: [T, ld] (the branch's columns start at x itself); u: [T, W]; conv_state: [slots, taps - 1, W], oldest first.
-template <typename T>
+// A thread owns a channel and TS consecutive rows of the step: its taps and the TS + taps - 1 inputs it needs are
+// read once.  Tap k of the design is slot k + kMaxTaps - taps here, so that every index is known at compile time.
+template <typename T, int TS>
 __global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, int64_t ld,
                                    const void* __restrict__ bx, const void* __restrict__ w,
                                    const void* __restrict__ bc, int w_dtype, const T* __restrict__ conv_state,
                                    const int* __restrict__ seq_of_token, const int* __restrict__ cu_q,
-                                   const int* __restrict__ state_slots, int W, int taps) {
+                                   const int* __restrict__ state_slots, int n_rows, int W, int taps) {
   atom::pdl_trigger();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t_base = blockIdx.x * TS;
+  if (c >= W) return;
+  const int skip = kMaxTaps - taps;
+  float wt[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) wt[k] = k >= skip ? load_as_float(w, w_dtype, (int64_t)c * taps + k - skip) : 0.f;
+  const float bias = load_as_float(bx, w_dtype, c), cbias = load_as_float(bc, w_dtype, c);
   atom::pdl_wait();
-  const int t = blockIdx.x;
-  const int s = seq_of_token[t];
-  if (s < 0) return;
-  const int first = cu_q[s];
-  const T* st = conv_state + (int64_t)state_slots[s] * (taps - 1) * W;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
-    const float bias = load_as_float(bx, w_dtype, c);
-    float acc = load_as_float(bc, w_dtype, c);
-    for (int k = 0; k < taps; ++k) {
-      const int i = t - (taps - 1) + k;
-      const float v = i >= first ? conv_input(x, ld, i, c, bias) : to_float(st[(int64_t)(taps - 1 + i - first) * W + c]);
-      acc = fmaf(load_as_float(w, w_dtype, (int64_t)c * taps + k), v, acc);
+  float xv[TS + kMaxTaps - 1];
+#pragma unroll
+  for (int j = 0; j < TS + kMaxTaps - 1; ++j) {
+    const int i = t_base - (kMaxTaps - 1) + j;
+    xv[j] = (j >= skip && i >= 0 && i < n_rows) ? conv_input(x, ld, i, c, bias) : 0.f;
+  }
+#pragma unroll
+  for (int tt = 0; tt < TS; ++tt) {
+    const int t = t_base + tt;
+    if (t >= n_rows) break;
+    const int s = seq_of_token[t];
+    if (s < 0) continue;
+    const int first = cu_q[s];
+    float acc = cbias;
+    if (t - (taps - 1) >= first) {
+#pragma unroll
+      for (int k = 0; k < kMaxTaps; ++k) acc = fmaf(wt[k], xv[tt + k], acc);
+    } else {      // the request's first rows of the step: what came before them is in its state
+      const T* st = conv_state + (int64_t)state_slots[s] * (taps - 1) * W;
+#pragma unroll
+      for (int k = 0; k < kMaxTaps; ++k) {
+        const int i = t - (kMaxTaps - 1) + k;
+        if (k < skip) continue;
+        const float v = i >= first ? xv[tt + k] : to_float(st[(int64_t)(taps - 1 + i - first) * W + c]);
+        acc = fmaf(wt[k], v, acc);
+      }
     }
     u[(int64_t)t * W + c] = from_float<T>(acc);
   }
@@ -61,10 +85,11 @@ __global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, i
 
 // gates: [T, blocks, 2 * bw] float (r's sums, then i's, per block of bw channels); gate_b: [blocks, 2 * bw];
 // y, x: [T, ld] columns of the two branches before bias; out: [T, W].
-// A block is 32 channels (the lanes) x NW warps; a request's tokens of the step are cut into NW runs, one per warp.
-// The recurrence is linear in S, so a run is summed up as S_end = A S_begin + B: every warp first finds (A, B) of its
-// run, the pairs of the runs before it give its S_begin, and a second walk writes the outputs.  Few tokens (a decoded
-// token above all) are walked once, by the first warp.
+// A block is cw channels (32, or 16 where long portions would otherwise leave SMs idle) x NW warps; a request's
+// tokens of the step are cut into runs, one per group of cw lanes.  The recurrence is linear in S, so a run is
+// summed up as S_end = A S_begin + B: every group first finds (A, B) of its run, the pairs of the runs before it give
+// its S_begin, and a second walk writes the outputs.  Few tokens (a decoded token above all) are walked once, by the
+// first group.
 constexpr int kScanOnce = 8;      // up to this many tokens of a request: one walk
 
 template <typename T>
@@ -73,12 +98,14 @@ rglru_scan_kernel(T* __restrict__ out, const float* __restrict__ gates, const vo
                   const void* __restrict__ lam, const T* __restrict__ u, const T* __restrict__ y,
                   const T* __restrict__ x, int64_t ld, const void* __restrict__ by, const void* __restrict__ bx,
                   int w_dtype, float* __restrict__ state, T* __restrict__ conv_state, const int* __restrict__ cu_q,
-                  const int* __restrict__ state_slots, int W, int bw, int taps, float decay_c, int write_state) {
+                  const int* __restrict__ state_slots, int W, int bw, int taps, float decay_c, int write_state,
+                  int cw) {
   atom::pdl_trigger();
-  __shared__ float sA[32][33], sB[32][33];
+  __shared__ float sA[64][33], sB[64][33];
   const int s = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
-  const int c = blockIdx.y * 32 + lane;
+  const int lane = threadIdx.x & 31, cl = lane & (cw - 1);
+  const int run = (threadIdx.x >> 5) * (32 / cw) + lane / cw, NR = (blockDim.x >> 5) * (32 / cw);
+  const int c = blockIdx.y * cw + cl;
   const bool live = c < W;
   const int b = live ? c / bw : 0, cb = live ? c - b * bw : 0;
   float sp = 0.f, br = 0.f, bi = 0.f, byc = 0.f, bxc = 0.f;
@@ -93,9 +120,9 @@ rglru_scan_kernel(T* __restrict__ out, const float* __restrict__ gates, const vo
   const int first = cu_q[s], last = cu_q[s + 1];
   const int n = last - first;
   if (n <= 0) return;
-  const bool once = n <= kScanOnce || NW == 1;
-  const int per = once ? n : (n + NW - 1) / NW;
-  const int t0 = min(last, first + warp * per), t1 = min(last, t0 + per);
+  const bool once = n <= kScanOnce || NR == 1;
+  const int per = once ? n : (n + NR - 1) / NR;
+  const int t0 = min(last, first + run * per), t1 = min(last, t0 + per);
   const int slot = state_slots[s];
   const int64_t goff = (int64_t)b * 2 * bw + cb;
 
@@ -118,10 +145,10 @@ rglru_scan_kernel(T* __restrict__ out, const float* __restrict__ gates, const vo
         A *= a;
         B = fmaf(a, B, bt);
       }
-    sA[warp][lane] = A;
-    sB[warp][lane] = B;
+    sA[run][cl] = A;
+    sB[run][cl] = B;
     __syncthreads();
-    for (int k = 0; k < warp; ++k) S = fmaf(sA[k][lane], S, sB[k][lane]);
+    for (int k = 0; k < run; ++k) S = fmaf(sA[k][cl], S, sB[k][cl]);
   }
   if (!live) return;
   for (int t = t0; t < t1; ++t) {
@@ -178,17 +205,21 @@ ATOM_EXPORT int atom_causal_conv(void* u, const void* x, int dtype, int64_t ld, 
   if (T <= 0) return ATOM_OK;
   if (W <= 0 || taps < 1 || taps > atom::kMaxTaps || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
   const int threads = 128;
-  int gy = (W + threads - 1) / threads;
-  if (gy > 64) gy = 64;
-  if (dtype == ATOM_F32)
-    atom::launch_pdl(atom::causal_conv_kernel<float>, dim3(T, gy), dim3(threads), 0, stream, (float*)u, (const float*)x,
-                     ld, bx, w, bc, w_dtype, (const float*)conv_state, seq_of_token, cu_q, state_slots, W, taps);
-  else if (dtype == ATOM_BF16)
-    atom::launch_pdl(atom::causal_conv_kernel<__nv_bfloat16>, dim3(T, gy), dim3(threads), 0, stream, (__nv_bfloat16*)u,
-                     (const __nv_bfloat16*)x, ld, bx, w, bc, w_dtype, (const __nv_bfloat16*)conv_state, seq_of_token,
-                     cu_q, state_slots, W, taps);
-  else
+  const int gy = (W + threads - 1) / threads;
+  if (gy > 65535) return ATOM_ERR_ARG;
+  // strips of 8 rows per thread in long steps, a row per thread in short ones (by the step's size alone)
+#define ATOM_CONV(TYPE, TS)                                                                                             \
+  atom::launch_pdl(atom::causal_conv_kernel<TYPE, TS>, dim3((T + TS - 1) / TS, gy), dim3(threads), 0, stream, (TYPE*)u, \
+                   (const TYPE*)x, ld, bx, w, bc, w_dtype, (const TYPE*)conv_state, seq_of_token, cu_q, state_slots, T, \
+                   W, taps)
+  if (dtype == ATOM_F32) {
+    if (T >= 256) ATOM_CONV(float, 8); else ATOM_CONV(float, 1);
+  } else if (dtype == ATOM_BF16) {
+    if (T >= 256) ATOM_CONV(__nv_bfloat16, 8); else ATOM_CONV(__nv_bfloat16, 1);
+  } else {
     return ATOM_ERR_ARG;
+  }
+#undef ATOM_CONV
   return atom::check_launch();
 }
 
@@ -202,16 +233,18 @@ ATOM_EXPORT int atom_rglru_scan(void* out, const float* gates, const void* gate_
     return ATOM_ERR_ARG;
   // warps along the tokens: by the step's size alone, so that a captured step replays the same launch
   const int threads = 32 * (T >= 512 ? 32 : (T >= 32 ? 8 : 1));
-  const dim3 grid(num_seqs, (W + 31) / 32);
+  const int cw = (T >= 512 && num_seqs * ((W + 31) / 32) < 148) ? 16 : 32;
+  const dim3 grid(num_seqs, (W + cw - 1) / cw);
   if (grid.y > 65535) return ATOM_ERR_ARG;
   if (dtype == ATOM_F32)
     atom::launch_pdl(atom::rglru_scan_kernel<float>, grid, dim3(threads), 0, stream, (float*)out, gates, gate_b, lam,
                      (const float*)u, (const float*)y, (const float*)x, ld, by, bx, w_dtype, state, (float*)conv_state,
-                     cu_q, state_slots, W, bw, taps, decay_c, write_state);
+                     cu_q, state_slots, W, bw, taps, decay_c, write_state, cw);
   else if (dtype == ATOM_BF16)
     atom::launch_pdl(atom::rglru_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)out, gates,
                      gate_b, lam, (const __nv_bfloat16*)u, (const __nv_bfloat16*)y, (const __nv_bfloat16*)x, ld, by, bx,
-                     w_dtype, state, (__nv_bfloat16*)conv_state, cu_q, state_slots, W, bw, taps, decay_c, write_state);
+                     w_dtype, state, (__nv_bfloat16*)conv_state, cu_q, state_slots, W, bw, taps, decay_c, write_state,
+                     cw);
   else
     return ATOM_ERR_ARG;
   return atom::check_launch();
