@@ -16,7 +16,7 @@
 
 namespace atom {
 
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 32;
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -35,8 +35,9 @@ __device__ __forceinline__ float conv_input(const T* x, int64_t ld, int64_t t, i
 
 // x: [T, ld] (the branch's columns start at x itself); u: [T, W]; conv_state: [slots, taps - 1, W], oldest first.
 // A thread owns a channel and TS consecutive rows of the step: its taps and the TS + taps - 1 inputs it needs are
-// read once.  Tap k of the design is slot k + kMaxTaps - taps here, so that every index is known at compile time.
-template <typename T, int TS>
+// read once.  Tap k of the design is slot k + KT - taps of KT >= taps here, so that every index is known at compile
+// time.
+template <typename T, int TS, int KT>
 __global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, int64_t ld,
                                    const void* __restrict__ bx, const void* __restrict__ w,
                                    const void* __restrict__ bc, int w_dtype, const T* __restrict__ conv_state,
@@ -46,16 +47,16 @@ __global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, i
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const int t_base = blockIdx.x * TS;
   if (c >= W) return;
-  const int skip = kMaxTaps - taps;
-  float wt[kMaxTaps];
+  const int skip = KT - taps;
+  float wt[KT];
 #pragma unroll
-  for (int k = 0; k < kMaxTaps; ++k) wt[k] = k >= skip ? load_as_float(w, w_dtype, (int64_t)c * taps + k - skip) : 0.f;
+  for (int k = 0; k < KT; ++k) wt[k] = k >= skip ? load_as_float(w, w_dtype, (int64_t)c * taps + k - skip) : 0.f;
   const float bias = load_as_float(bx, w_dtype, c), cbias = load_as_float(bc, w_dtype, c);
   atom::pdl_wait();
-  float xv[TS + kMaxTaps - 1];
+  float xv[TS + KT - 1];
 #pragma unroll
-  for (int j = 0; j < TS + kMaxTaps - 1; ++j) {
-    const int i = t_base - (kMaxTaps - 1) + j;
+  for (int j = 0; j < TS + KT - 1; ++j) {
+    const int i = t_base - (KT - 1) + j;
     xv[j] = (j >= skip && i >= 0 && i < n_rows) ? conv_input(x, ld, i, c, bias) : 0.f;
   }
 #pragma unroll
@@ -68,12 +69,12 @@ __global__ void causal_conv_kernel(T* __restrict__ u, const T* __restrict__ x, i
     float acc = cbias;
     if (t - (taps - 1) >= first) {
 #pragma unroll
-      for (int k = 0; k < kMaxTaps; ++k) acc = fmaf(wt[k], xv[tt + k], acc);
+      for (int k = 0; k < KT; ++k) acc = fmaf(wt[k], xv[tt + k], acc);
     } else {      // the request's first rows of the step: what came before them is in its state
       const T* st = conv_state + (int64_t)state_slots[s] * (taps - 1) * W;
 #pragma unroll
-      for (int k = 0; k < kMaxTaps; ++k) {
-        const int i = t - (kMaxTaps - 1) + k;
+      for (int k = 0; k < KT; ++k) {
+        const int i = t - (KT - 1) + k;
         if (k < skip) continue;
         const float v = i >= first ? xv[tt + k] : to_float(st[(int64_t)(taps - 1 + i - first) * W + c]);
         acc = fmaf(wt[k], v, acc);
@@ -207,18 +208,26 @@ ATOM_EXPORT int atom_causal_conv(void* u, const void* x, int dtype, int64_t ld, 
   const int threads = 128;
   const int gy = (W + threads - 1) / threads;
   if (gy > 65535) return ATOM_ERR_ARG;
-  // strips of 8 rows per thread in long steps, a row per thread in short ones (by the step's size alone)
-#define ATOM_CONV(TYPE, TS)                                                                                             \
-  atom::launch_pdl(atom::causal_conv_kernel<TYPE, TS>, dim3((T + TS - 1) / TS, gy), dim3(threads), 0, stream, (TYPE*)u, \
-                   (const TYPE*)x, ld, bx, w, bc, w_dtype, (const TYPE*)conv_state, seq_of_token, cu_q, state_slots, T, \
-                   W, taps)
-  if (dtype == ATOM_F32) {
-    if (T >= 256) ATOM_CONV(float, 8); else ATOM_CONV(float, 1);
-  } else if (dtype == ATOM_BF16) {
-    if (T >= 256) ATOM_CONV(__nv_bfloat16, 8); else ATOM_CONV(__nv_bfloat16, 1);
-  } else {
-    return ATOM_ERR_ARG;
-  }
+  // strips of 8 rows per thread in long steps, a row per thread in short ones (by the step's size alone); tap slots
+  // in steps of 8, 16, 32
+#define ATOM_CONV(TYPE, TS, KT)                                                                                         \
+  atom::launch_pdl(atom::causal_conv_kernel<TYPE, TS, KT>, dim3((T + TS - 1) / TS, gy), dim3(threads), 0, stream,       \
+                   (TYPE*)u, (const TYPE*)x, ld, bx, w, bc, w_dtype, (const TYPE*)conv_state, seq_of_token, cu_q,       \
+                   state_slots, T, W, taps)
+#define ATOM_CONV_T(TYPE)                                                    \
+  do {                                                                       \
+    if (taps <= 8) {                                                         \
+      if (T >= 256) ATOM_CONV(TYPE, 8, 8); else ATOM_CONV(TYPE, 1, 8);       \
+    } else if (taps <= 16) {                                                 \
+      if (T >= 256) ATOM_CONV(TYPE, 8, 16); else ATOM_CONV(TYPE, 1, 16);     \
+    } else {                                                                 \
+      if (T >= 256) ATOM_CONV(TYPE, 4, 32); else ATOM_CONV(TYPE, 1, 32);     \
+    }                                                                        \
+  } while (0)
+  if (dtype == ATOM_F32) ATOM_CONV_T(float);
+  else if (dtype == ATOM_BF16) ATOM_CONV_T(__nv_bfloat16);
+  else return ATOM_ERR_ARG;
+#undef ATOM_CONV_T
 #undef ATOM_CONV
   return atom::check_launch();
 }

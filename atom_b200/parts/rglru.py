@@ -31,8 +31,8 @@ class GatedLinearRecurrence(Mixer):
     def __init__(self, hidden_size: int, width: int, blocks: int, taps: int, decay: float = 8.0):
         if width % blocks:
             raise ValueError(f"rglru: width {width} is no multiple of its {blocks} blocks")
-        if not 1 <= taps <= 8:
-            raise ValueError(f"rglru: {taps} taps are beyond what the kernel takes (1 to 8)")
+        if not 1 <= taps <= 32:
+            raise ValueError(f"rglru: {taps} taps are beyond what the kernels take (1 to 32)")
         self.hidden_size, self.width, self.blocks, self.taps, self.decay = hidden_size, width, blocks, taps, float(decay)
 
     def params(self) -> Dict[str, ParamSpec]:

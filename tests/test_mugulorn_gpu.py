@@ -232,16 +232,21 @@ def test_sink_counts_once_has_no_value_and_is_not_scaled(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("W,blocks,taps", [(96, 3, 3), (128, 1, 2), (60, 5, 1), (140, 4, 8), (384, 4, 4), (80, 80, 4)])
-def test_convolution_and_recurrence_carry_over_steps(W, blocks, taps, dtype):
+@pytest.mark.parametrize("W,blocks,taps,lens", [
+    (96, 3, 3, (37, 5, 18)), (128, 1, 2, (37, 5, 18)), (60, 5, 1, (37, 5, 18)), (140, 4, 8, (37, 5, 18)),
+    (384, 4, 4, (37, 5, 18)), (80, 80, 4, (37, 5, 18)),
+    (64, 2, 4, (300, 5, 40)), (48, 3, 12, (37, 5, 18)), (40, 2, 20, (290, 9, 4)), (72, 1, 7, (3, 530, 2))])
+def test_convolution_and_recurrence_carry_over_steps(W, blocks, taps, lens, dtype):
     """Three requests of unequal lengths in one batch, fed whole, token by token and in portions down to two tokens,
-    on state slots that held other requests before: the convolution's tail and the state go from step to step."""
+    on state slots that held other requests before: the convolution's tail and the state go from step to step.  The
+    long requests reach the kernels' forms for long steps (strips of rows, runs of a request side by side), the many
+    taps the wider tap slots."""
     from atom_b200 import native
 
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(W + taps)
     bw = W // blocks
-    lens = [37, 5, 18]
+    lens = list(lens)
     P = {"y.b": torch.randn(W, generator=g) * 0.3, "x.b": torch.randn(W, generator=g) * 0.3,
          "conv": torch.randn(W, taps, generator=g) * 0.5, "conv.b": torch.randn(W, generator=g) * 0.2,
          "ra": torch.randn(blocks, bw, bw, generator=g) / bw ** 0.5, "ra.b": torch.randn(blocks, bw, generator=g),
@@ -271,7 +276,7 @@ def test_convolution_and_recurrence_carry_over_steps(W, blocks, taps, dtype):
 
     want = [reference(p) for p in proj]
     n_slots = 5
-    for cuts in ([100], [1], [2], [7, 2, 3]):
+    for cuts in ([1000], [1], [2], [7, 2, 3]) if max(lens) < 100 else ([1000], [270, 2, 1], [7, 280, 3]):
         state = torch.randn(n_slots, W, device=DEV)                       # what earlier requests left behind
         conv_state = torch.randn(n_slots, max(taps - 1, 1), W, device=DEV).to(dt)[:, :taps - 1].contiguous()
         slots = [3, 0, 4]
