@@ -70,6 +70,12 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
   float* ms = Ss + kSlices * kTcRows * kTcSStride;                                // [rows]
   float* ls = ms + kTcRows;
   float* cs = ls + kTcRows;
+  // MI == 4 keeps its scores in registers; where they would lie are two halves' row maxima and sums, and the running
+  // maximum twice (read from one, written to the other, so that both warps of a row read the same old value)
+  float* pm = Ss;                      // [rows][2]
+  float* psum = pm + 2 * kTcRows;      // [rows][2]
+  if (MI == 4) ms = psum + 2 * kTcRows;     // [2][rows]
+  int par = 0;
 
   // which request and which of its tokens this CTA owns (read from the step's arrays: written before the step)
   int idx = blockIdx.x, s = 0, tok0 = -1, ntok = 0;
@@ -132,6 +138,7 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
   }
   for (int i = tid; i < kTcRows; i += kTcThreads) {
     ms[i] = -INFINITY;
+    if (MI == 4) ms[kTcRows + i] = -INFINITY;
     ls[i] = 0.f;
   }
   float acc[MI][NT][4];
@@ -182,46 +189,106 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
       for (int n2 = 0; n2 < 2; ++n2)
 #pragma unroll
         for (int e = 0; e < 4; ++e) sc[n2][e] += sd[n2][e];
+      if constexpr (MI == 4) {
+        // softmax on the fragments: a thread holds rows g and g + 8 of its warp's tile at keys nb + 8 n2 + 2 t4 + e;
+        // the row's other keys are in its three neighbours of the quad and in the warp beside this one
+        const int half_of_row = warp & 1;
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int n2 = 0; n2 < 2; ++n2) {
-        float* d0 = Ss + (slice * kTcRows + mi * 16 + g) * kTcSStride + nb + n2 * 8 + 2 * t4;
-        d0[0] = sc[n2][0];
-        d0[1] = sc[n2][1];
-        d0[8 * kTcSStride] = sc[n2][2];
-        d0[8 * kTcSStride + 1] = sc[n2][3];
-      }
-    }
-    __syncthreads();
-    {   // softmax: warp w owns rows 2 MI w .. 2 MI (w + 1) - 1, a lane is a key
-      const int key = k0 + lane;
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = mi * 16 + g + 8 * hf;
+          const int ti = r / HG;
+          const int p = p0 + ti;
 #pragma unroll
-      for (int rr = 0; rr < 2 * MI; ++rr) {
-        const int r = warp * 2 * MI + rr;
-        const int ti = r / HG;
-        const int p = p0 + ti;
-        const bool seen = ti < ntok && key <= p && key <= k_hi && (window <= 0 || p - key < window);
-        float raw = Ss[r * kTcSStride + lane];
+          for (int n2 = 0; n2 < 2; ++n2)
 #pragma unroll
-        for (int sl = 1; sl < kSlices; ++sl) raw += Ss[(sl * kTcRows + r) * kTcSStride + lane];
-        const float sc = seen ? raw * scale : -INFINITY;
-        const float m_old = ms[r];
-        const float m_new = fmaxf(m_old, warp_max(sc));
-        const float pw = (sc == -INFINITY) ? 0.f : expf(sc - m_new);
-        const float sum = warp_sum(pw);
-        const __nv_bfloat16 hi = __float2bfloat16_rn(pw);
-        Ph[r * kTcPStride + lane] = hi;
-        Pl[r * kTcPStride + lane] = __float2bfloat16_rn(pw - __bfloat162float(hi));
-        __syncwarp();
-        if (lane == 0) {
-          const float corr = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
-          cs[r] = (m_new == -INFINITY) ? 1.f : corr;
-          ms[r] = m_new;
-          ls[r] = ls[r] * corr + sum;
+            for (int e = 0; e < 2; ++e) {
+              const int key = k0 + nb + n2 * 8 + 2 * t4 + e;
+              const bool seen = ti < ntok && key <= p && key <= k_hi && (window <= 0 || p - key < window);
+              const float v = seen ? sc[n2][2 * hf + e] * scale : -INFINITY;
+              sc[n2][2 * hf + e] = v;
+              mx[hf] = fmaxf(mx[hf], v);
+            }
+          mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+          mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+          if (t4 == 0) pm[r * 2 + half_of_row] = mx[hf];
+        }
+        __syncthreads();
+        const float* m_cur = ms + par * kTcRows;
+        float* m_nxt = ms + (par ^ 1) * kTcRows;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = mi * 16 + g + 8 * hf;
+          const float m_old = m_cur[r];
+          const float m_new = fmaxf(m_old, fmaxf(pm[r * 2], pm[r * 2 + 1]));
+          float sum = 0.f;
+#pragma unroll
+          for (int n2 = 0; n2 < 2; ++n2) {
+            const float w0 = sc[n2][2 * hf] == -INFINITY ? 0.f : expf(sc[n2][2 * hf] - m_new);
+            const float w1 = sc[n2][2 * hf + 1] == -INFINITY ? 0.f : expf(sc[n2][2 * hf + 1] - m_new);
+            sum += w0 + w1;
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(w0 - __low2float(hi), w1 - __high2float(hi));
+            const int at = r * kTcPStride + nb + n2 * 8 + 2 * t4;
+            *reinterpret_cast<__nv_bfloat162*>(Ph + at) = hi;
+            *reinterpret_cast<__nv_bfloat162*>(Pl + at) = lo;
+          }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          if (t4 == 0) {
+            psum[r * 2 + half_of_row] = sum;
+            if (half_of_row == 0) {
+              const float corr = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+              cs[r] = (m_new == -INFINITY) ? 1.f : corr;
+              m_nxt[r] = m_new;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int n2 = 0; n2 < 2; ++n2) {
+          float* d0 = Ss + (slice * kTcRows + mi * 16 + g) * kTcSStride + nb + n2 * 8 + 2 * t4;
+          d0[0] = sc[n2][0];
+          d0[1] = sc[n2][1];
+          d0[8 * kTcSStride] = sc[n2][2];
+          d0[8 * kTcSStride + 1] = sc[n2][3];
+        }
+        __syncthreads();
+        // softmax: warp w owns rows 2 w and 2 w + 1, a lane is a key; the slices' partial scores are added here
+        const int key = k0 + lane;
+#pragma unroll
+        for (int rr = 0; rr < 2 * MI; ++rr) {
+          const int r = warp * 2 * MI + rr;
+          const int ti = r / HG;
+          const int p = p0 + ti;
+          const bool seen = ti < ntok && key <= p && key <= k_hi && (window <= 0 || p - key < window);
+          float raw = Ss[r * kTcSStride + lane];
+#pragma unroll
+          for (int sl = 1; sl < kSlices; ++sl) raw += Ss[(sl * kTcRows + r) * kTcSStride + lane];
+          const float sv = seen ? raw * scale : -INFINITY;
+          const float m_old = ms[r];
+          const float m_new = fmaxf(m_old, warp_max(sv));
+          const float pw = (sv == -INFINITY) ? 0.f : expf(sv - m_new);
+          const float sum = warp_sum(pw);
+          const __nv_bfloat16 hi = __float2bfloat16_rn(pw);
+          Ph[r * kTcPStride + lane] = hi;
+          Pl[r * kTcPStride + lane] = __float2bfloat16_rn(pw - __bfloat162float(hi));
+          __syncwarp();
+          if (lane == 0) {
+            const float corr = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+            cs[r] = (m_new == -INFINITY) ? 1.f : corr;
+            ms[r] = m_new;
+            ls[r] = ls[r] * corr + sum;
+          }
         }
       }
     }
     __syncthreads();
     {   // output: this warp's R / 8 columns of all rows
+      if (MI == 4) {
+        par ^= 1;
+        if (tid < kTcRows) ls[tid] = ls[tid] * cs[tid] + psum[2 * tid] + psum[2 * tid + 1];
+      }
       float c[MI][2];
 #pragma unroll
       for (int mi = 0; mi < MI; ++mi) {
@@ -276,12 +343,12 @@ latent_attention_tc_kernel(__nv_bfloat16* __restrict__ out, const float* __restr
           *reinterpret_cast<float2*>(dst + warp * 8 * NT + nt * 8 + 2 * t4) =
               make_float2(acc[mi][nt][half * 2], acc[mi][nt][half * 2 + 1]);
         if (warp == 0 && t4 == 0) {
-          dst[R] = ms[r];
+          dst[R] = ms[par * kTcRows + r];
           dst[R + 1] = ls[r];
         }
         continue;
       }
-      const float m = ms[r], sk = sink ? sink[h0 + hi] : -INFINITY;
+      const float m = ms[par * kTcRows + r], sk = sink ? sink[h0 + hi] : -INFINITY;
       const float top = fmaxf(m, sk);
       const float w = expf(m - top);
       const float inv = w / (ls[r] * w + (sink ? expf(sk - top) : 0.f));
