@@ -136,7 +136,7 @@ def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0
 
 LATENT_CASES = [  # H, R, rd, window, page, T
     (4, 32, 8, 24, 16, 70), (2, 48, 16, 7, 8, 40), (3, 16, 4, 0, 8, 100), (5, 36, 12, 1, 16, 20), (1, 60, 20, 33, 16, 90),
-    (8, 128, 32, 128, 32, 300), (16, 512, 64, 64, 64, 130), (6, 64, 16, 50, 16, 170), (3, 256, 0, 0, 16, 150),
+    (8, 128, 32, 128, 32, 300), (16, 512, 64, 64, 64, 130), (7, 64, 32, 50, 16, 170), (3, 256, 0, 0, 16, 150),
     (70, 64, 32, 40, 8, 90),
 ]
 
@@ -167,7 +167,7 @@ def test_latent_attention_in_prompts_portions_and_decoding(case, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nsplit", [2, 3, 7, 40])
 def test_latent_attention_with_keys_shared_out_among_blocks(nsplit, dtype):
-    H, R, rd, window, page, T = 4, 64, 16, 0, 16, 333
+    H, R, rd, window, page, T = 4, 64, 48, 0, 16, 333
     g = torch.Generator().manual_seed(nsplit)
     q = torch.randn(T, H, R + rd, generator=g).double()
     rows = _rounded(torch.randn(T, R + rd, generator=g), dtype)
@@ -185,7 +185,7 @@ def test_one_key_at_the_windows_edge_stands_out(window, dtype):
     """One key row carries a mark that only it has and a score far above all others.  Queries at distance window - 1
     find the mark, queries at distance window do not: in a prompt, across portions that end at every place around
     the edge and a page's border, and decoded one by one."""
-    H, R, rd, page, T = 2, 64, 16, 16, 420
+    H, R, rd, page, T = 2, 64, 32, 16, 420
     needle = 77
     g = torch.Generator().manual_seed(window)
     rows = torch.randn(T, R + rd, generator=g) * 0.1
@@ -217,7 +217,7 @@ def test_one_key_at_the_windows_edge_stands_out(window, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sink_counts_once_has_no_value_and_is_not_scaled(dtype):
     """With one key, the weight of its row is 1 / (1 + exp(sink - score)); a large sink empties the output."""
-    H, R, rd = 3, 64, 16
+    H, R, rd = 3, 128, 16
     rows = _rounded(torch.ones(1, R + rd), dtype)
     q = torch.zeros(1, H, R + rd).double()
     q[:, :, 0] = torch.tensor([0.0, 1.0, -2.0]).double()
