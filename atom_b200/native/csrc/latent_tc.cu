@@ -4,10 +4,11 @@
 // steps of single tokens), and walks the keys its tokens may see, or its share of them, in tiles of 32:
 //   1. the tile's rows come into shared memory once (cp.async, two buffers): they are the K operand of the
 //      scores AND, in their first R columns, the V operand of the output;
-//   2. S[64 x 32] = Q K^T on mma.sync m16n8k16 (each warp two 16 x 8 tiles over all R + rd columns), 32-bit
-//      sums to shared memory;
-//   3. warp w owns rows 8w .. 8w + 7: scale, window and causal mask, running maximum and sum per row in 32-bit,
-//      the weights written back as two bfloat16 numbers p = hi + lo (16 bits of mantissa);
+//   2. S[64 x 32] = Q K^T on mma.sync m16n8k16 (each warp two 16 x 8 tiles over all R + rd columns), 32-bit sums;
+//   3. scale, window and causal mask, running maximum and sum per row in 32-bit.  64-row tiles do this on the
+//      score fragments (a row's statistics through the quads and one exchange between the two warps that hold the
+//      row); 16-row tiles add the warps' partial scores in shared memory, a warp per two rows and a lane per key.
+//      The weights go to shared memory as two bfloat16 numbers p = hi + lo (16 bits of mantissa);
 //   4. O[64 x R] = O * corr + (P_hi + P_lo) V: warp w owns R / 8 columns of all 64 rows in registers.
 // The learned sink enters the denominator at the end, or in the merge kernel when the keys were shared out.
 // Tiles are found from cu_q on the device, so the launch depends on the step's shape alone.
@@ -388,7 +389,7 @@ static int launch_latent_tc(__nv_bfloat16* out, const float* q, const __nv_bfloa
 
 ATOM_EXPORT int atom_latent_attention_tc_supports(int H, int R, int rd) {
   if (H <= 0 || rd < 0 || rd % 16) return 0;
-  if (R != 64 && R != 128 && R != 256 && R != 512) return 0;
+  if (R < 64 || R > 512 || R % 64) return 0;
   return atom::latent_tc_smem(R, rd, 64) <= 220 * 1024;
 }
 
@@ -413,7 +414,11 @@ ATOM_EXPORT int atom_latent_attention_tc(void* out, const float* q, const void* 
   switch (R) {
     case 64: ATOM_LATENT_TC(1);
     case 128: ATOM_LATENT_TC(2);
+    case 192: ATOM_LATENT_TC(3);
     case 256: ATOM_LATENT_TC(4);
+    case 320: ATOM_LATENT_TC(5);
+    case 384: ATOM_LATENT_TC(6);
+    case 448: ATOM_LATENT_TC(7);
     case 512: ATOM_LATENT_TC(8);
   }
 #undef ATOM_LATENT_TC

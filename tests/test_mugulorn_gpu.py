@@ -137,7 +137,7 @@ def _run_latent(q, rows, R, rd, scale, window, sink, dtype, page, cuts, nsplit=0
 LATENT_CASES = [  # H, R, rd, window, page, T
     (4, 32, 8, 24, 16, 70), (2, 48, 16, 7, 8, 40), (3, 16, 4, 0, 8, 100), (5, 36, 12, 1, 16, 20), (1, 60, 20, 33, 16, 90),
     (8, 128, 32, 128, 32, 300), (16, 512, 64, 64, 64, 130), (7, 64, 32, 50, 16, 170), (3, 256, 0, 0, 16, 150),
-    (70, 64, 32, 40, 8, 90),
+    (70, 64, 32, 40, 8, 90), (5, 192, 32, 100, 16, 230), (2, 320, 16, 0, 32, 150),
 ]
 
 
