@@ -13,6 +13,7 @@
 //   rglru_scan_kernel    a request's tokens of the step in runs, one warp per run and one lane per channel; then S
 //                        and the last taps - 1 values of v go back to the state row
 #include "common.cuh"
+#include <cstdint>
 
 namespace atom {
 
@@ -198,6 +199,51 @@ __global__ void gelu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   }
 }
 
+// The two kernels above for bfloat16 rows of a multiple of 8 numbers at 16-byte-aligned places: 16 bytes per load.
+__global__ void sigmoid_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g, int64_t ld,
+                                            int64_t nvec, int n8) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec; idx += stride) {
+    const int64_t t = idx / n8;
+    const int i = (int)(idx - t * n8);
+    uint4 x4 = *reinterpret_cast<const uint4*>(x + idx * 8);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(g + t * ld + (int64_t)i * 8);
+    __nv_bfloat162* xh = reinterpret_cast<__nv_bfloat162*>(&x4);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xh[e]), b = __bfloat1622float2(gh[e]);
+      xh[e] = __floats2bfloat162_rn(a.x * sigmoid_f(b.x), a.y * sigmoid_f(b.y));
+    }
+    *reinterpret_cast<uint4*>(x + idx * 8) = x4;
+  }
+}
+
+__global__ void gelu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
+                                         int64_t nvec, int I8) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec; idx += stride) {
+    const int64_t t = idx / I8;
+    const int i = (int)(idx - t * I8);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + i) * 8);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + I8 + i) * 8);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(gh[e]), b = __bfloat1622float2(uh[e]);
+      oh[e] = __floats2bfloat162_rn(gelu_tanh_f(a.x) * b.x, gelu_tanh_f(a.y) * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = o4;
+  }
+}
+
 }  // namespace atom
 
 ATOM_EXPORT int atom_causal_conv(void* u, const void* x, int dtype, int64_t ld, const void* bx, const void* w,
@@ -264,6 +310,14 @@ ATOM_EXPORT int atom_sigmoid_mul(void* x, const void* g, int dtype, int64_t ld, 
   const int64_t total = (int64_t)T * n;
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_BF16 && n % 8 == 0 && ld % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)g % 16 == 0) {
+    const int64_t nvec = total / 8;
+    int64_t vb = (nvec + 255) / 256;
+    if (vb > 148 * 32) vb = 148 * 32;
+    atom::launch_pdl(atom::sigmoid_mul_bf16_vec_kernel, dim3((int)vb), dim3(256), 0, stream, (__nv_bfloat16*)x,
+                     (const __nv_bfloat16*)g, ld, nvec, n / 8);
+    return atom::check_launch();
+  }
   if (dtype == ATOM_F32)
     atom::launch_pdl(atom::sigmoid_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)x, (const float*)g, ld, total, n);
   else if (dtype == ATOM_BF16)
@@ -279,6 +333,14 @@ ATOM_EXPORT int atom_gelu_mul(void* out, const void* gu, int dtype, int T, int I
   const int64_t n = (int64_t)T * I;
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ATOM_BF16 && I % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gu % 16 == 0) {
+    const int64_t nvec = n / 8;
+    int64_t vb = (nvec + 255) / 256;
+    if (vb > 148 * 32) vb = 148 * 32;
+    atom::launch_pdl(atom::gelu_mul_bf16_vec_kernel, dim3((int)vb), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)gu, nvec, I / 8);
+    return atom::check_launch();
+  }
   if (dtype == ATOM_F32)
     atom::launch_pdl(atom::gelu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gu, n, I);
   else if (dtype == ATOM_BF16)

@@ -354,16 +354,18 @@ def test_small_kernels(dtype):
 
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(1)
-    gu = _rounded(torch.randn(7, 2 * 52, generator=g) * 3, dtype)
-    out = torch.empty(7, 52, dtype=dt, device=DEV)
-    native.gelu_mul(out, gu.to(dt).to(DEV))
-    _close(out, plain.gelu_tanh(gu[:, :52]) * gu[:, 52:], dtype, "gelu_mul")
+    for n in (52, 72):        # 72: the form with 16-byte loads
+        gu = _rounded(torch.randn(7, 2 * n, generator=g) * 3, dtype)
+        out = torch.empty(7, n, dtype=dt, device=DEV)
+        native.gelu_mul(out, gu.to(dt).to(DEV))
+        _close(out, plain.gelu_tanh(gu[:, :n]) * gu[:, n:], dtype, f"gelu_mul {n}")
 
-    wide = _rounded(torch.randn(5, 100, generator=g) * 3, dtype)
-    x = _rounded(torch.randn(5, 30, generator=g), dtype)
-    xd = x.to(dt).to(DEV).contiguous()
-    native.sigmoid_mul(xd, wide.to(dt).to(DEV)[:, 70:])
-    _close(xd, x * torch.sigmoid(wide[:, 70:]), dtype, "sigmoid_mul")
+    for width, at, n in ((100, 70, 30), (104, 64, 40)):       # the second: the form with 16-byte loads
+        wide = _rounded(torch.randn(5, width, generator=g) * 3, dtype)
+        x = _rounded(torch.randn(5, n, generator=g), dtype)
+        xd = x.to(dt).to(DEV).contiguous()
+        native.sigmoid_mul(xd, wide.to(dt).to(DEV)[:, at:])
+        _close(xd, x * torch.sigmoid(wide[:, at:]), dtype, f"sigmoid_mul {n}")
 
     res = torch.randn(6, 100, generator=g)
     delta = _rounded(torch.randn(6, 100, generator=g), dtype)
