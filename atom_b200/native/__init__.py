@@ -802,7 +802,8 @@ class _RowsOpC(ctypes.Structure):
     _fields_ = [("X", _vp), ("lda", _i64), ("W", _vp), ("out", _vp), ("out_dtype", _i), ("ldc", _i64),
                 ("bias", _vp), ("bias_dtype", _i), ("N", _i), ("K", _i), ("gated", _i),
                 ("ssq_in", _vp), ("ssq_parts", _i), ("norm_size", _i), ("norm_eps", _f),
-                ("residual", _vp), ("norm_w", _vp), ("norm_w_dtype", _i), ("xout", _vp), ("ssq_out", _vp)]
+                ("residual", _vp), ("norm_w", _vp), ("norm_w_dtype", _i), ("xout", _vp), ("ssq_out", _vp),
+                ("res_scale", _f)]
 
 
 ROWS_M = 16     # rows up to which the weight-streaming product is used (parts/linear.py: streams)
@@ -821,11 +822,11 @@ def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
               bias: Optional[torch.Tensor] = None, gated: bool = False, ssq_in: Optional[torch.Tensor] = None,
               norm_size: int = 0, norm_eps: float = 0.0, residual: Optional[torch.Tensor] = None,
               norm_w: Optional[torch.Tensor] = None, xout: Optional[torch.Tensor] = None,
-              ssq_out: Optional[torch.Tensor] = None, act: str = "silu") -> None:
+              ssq_out: Optional[torch.Tensor] = None, act: str = "silu", res_scale: float = 1.0) -> None:
     """out[M, N] = x[M, K] w[N, K]^T for at most 16 rows of bf16 x, with one of the epilogues of
     csrc/gemm_rows.h: plain (+ bias; out bf16 or float32); ``gated`` (w = [gate ; up] of 2N rows, ``act`` "silu" or
     "gelu_tanh" on the gate);
-    ``residual`` (float32 [M, N], += product in place, with ``xout`` = bf16(residual * norm_w) and the CTAs'
+    ``residual`` (float32 [M, N], += ``res_scale`` * product in place, with ``xout`` = bf16(residual * norm_w) and the CTAs'
     sums of squares in ``ssq_out`` [gemm_rows_grid(), 16]).  ``ssq_in`` (such sums, of ``norm_size`` columns):
     every output row is first multiplied by its rstd."""
     M, K = x.shape
@@ -856,6 +857,7 @@ def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     c.residual, c.norm_w = _ptr(residual), _ptr(norm_w)
     c.norm_w_dtype = dtype_code(norm_w.dtype) if norm_w is not None else F32
     c.xout, c.ssq_out = _ptr(xout), _ptr(ssq_out)
+    c.res_scale = float(res_scale)
     _check(lib().atom_gemm_rows(ctypes.byref(c), M, error_flag(x.device).data_ptr(), _stream()), "gemm_rows")
 
 

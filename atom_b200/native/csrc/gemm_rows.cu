@@ -98,6 +98,7 @@ struct Params {
   int norm_w_dtype;
   __nv_bfloat16* xout;
   float* ssq_out;
+  float res_scale;
 };
 
 __device__ __forceinline__ int row_begin(const Params& p, int c) { return (int)((long long)p.N * c / gridDim.x); }
@@ -372,7 +373,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (my_row && m < p.M) {
         if (res_mode) {
           const int64_t at = (int64_t)m * p.N + col;
-          const float rr = old[nt] + sum;
+          const float rr = fmaf(p.res_scale, sum, old[nt]);
           p.residual[at] = rr;
           p.xout[at] = __float2bfloat16_rn(rr * nw);
           sq[nt] += rr * rr;
@@ -498,5 +499,6 @@ ATOM_EXPORT int atom_gemm_rows(const AtomRowsOp* op, int M, int* error, cudaStre
   p.norm_w_dtype = a.norm_w_dtype;
   p.xout = reinterpret_cast<__nv_bfloat16*>(a.xout);
   p.ssq_out = a.ssq_out;
+  p.res_scale = a.res_scale;
   return MT == 1 ? launch<1>(mw, mx, p, grid, stream) : launch<2>(mw, mx, p, grid, stream);
 }

@@ -30,4 +30,5 @@ typedef struct AtomRowsOp {
   int norm_w_dtype;
   void* xout;
   float* ssq_out;
+  float res_scale;   // residual epilogue: residual += res_scale * product
 } AtomRowsOp;

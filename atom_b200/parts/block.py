@@ -29,10 +29,10 @@ from .linear import resolve
 from .registry import register
 
 
-def _add_norm(norm, residual, delta, tag, receiver):
+def _add_norm(norm, residual, delta, tag, receiver, **kw):
     if getattr(norm, "fuses_products", False):
-        return norm.add_norm(residual, delta, tag, scaled_ok=getattr(receiver, "takes_scaled_rows", False))
-    return norm.add_norm(residual, resolve(delta), tag)
+        return norm.add_norm(residual, delta, tag, scaled_ok=getattr(receiver, "takes_scaled_rows", False), **kw)
+    return norm.add_norm(residual, resolve(delta), tag, **kw)
 
 
 def _forward(part, *args):
@@ -63,7 +63,7 @@ class PreNormBlock:
 class ScaledPreNormBlock:
     slots = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
     optional = ("ffn_norm", "ffn")
-    takes_pending = False
+    takes_pending = True      # delta may be a PendingProduct, and so may what run() returns
 
     def __init__(self, mixer_norm, mixer, ffn_norm=None, ffn=None, residual_mult: float = 1.0):
         if (ffn is None) != (ffn_norm is None):
@@ -74,13 +74,13 @@ class ScaledPreNormBlock:
     def run(self, residual, delta, step, cache, writes_cache, delta_scale=None):
         """delta_scale: the factor of the incoming delta (the block's own constant unless the model says otherwise)."""
         m = self.delta_scale
-        a = self.mixer_norm.add_norm(residual, resolve(delta), "norm.mixer",
-                                     delta_scale=m if delta_scale is None else delta_scale)
-        x = self.mixer.forward(a, step, cache, writes_cache)
+        a = _add_norm(self.mixer_norm, residual, delta, "norm.mixer", self.mixer,
+                      delta_scale=m if delta_scale is None else delta_scale)
+        x = _forward(self.mixer, a, step, cache, writes_cache)
         if self.ffn is None:
             return x
-        b = self.ffn_norm.add_norm(residual, x, "norm.ffn", delta_scale=m)
-        return self.ffn.forward(b, step)
+        b = _add_norm(self.ffn_norm, residual, x, "norm.ffn", self.ffn, delta_scale=m)
+        return _forward(self.ffn, b, step)
 
 
 @register("arrangement", "parallel")

@@ -26,7 +26,7 @@ import torch
 from .. import native
 from . import registry
 from .base import Mixer
-from .linear import linear
+from .linear import PendingProduct, linear, may_defer
 from .registry import register
 from .spec import CacheEntry, CacheNeed, ParamSpec, PartSpec
 
@@ -34,6 +34,8 @@ from .spec import CacheEntry, CacheNeed, ParamSpec, PartSpec
 @register("mixer", "latent_attention")
 class LatentAttention(Mixer):
     graph_safe = True
+    takes_scaled_rows = True      # x may be ScaledRows: the stacked first product finishes the norm
+    defers_output = True          # forward(..., defer=True) may hand the output projection on unrun
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, q_rank: int,
                  kv_rank: int, scale: float, norm_eps: float, position: PartSpec, window: Optional[int] = None,
@@ -108,7 +110,7 @@ class LatentAttention(Mixer):
             plan = step.plans[key] = (rows, native.attention_mixed_splits(units, longest, per_sm=per_sm, min_share=share))
         return plan
 
-    def forward(self, x, step, cache, writes_cache):
+    def forward(self, x, step, cache, writes_cache, defer=False):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
         H, dn, rd, dv, R, Rq = self.nh, self.dn, self.rd, self.dv, self.R, self.q_rank
@@ -147,7 +149,10 @@ class LatentAttention(Mixer):
         if self.gate:
             g_off = sum(rows) - H * dv
             native.sigmoid_mul(heads, proj[:, g_off:])
-        return linear(heads, self.w_o_weight, None, ws.get("lat.out", (T, self.hidden_size), dt))
+        out = ws.get("lat.out", (T, self.hidden_size), dt)
+        if defer and may_defer(heads, self.w_o_weight):
+            return PendingProduct(heads, self.w_o_weight, None, out)
+        return linear(heads, self.w_o_weight, None, out)
 
 
 def native_supports(heads: int, kv_rank: int, rot_dim: int) -> bool:

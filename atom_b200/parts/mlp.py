@@ -46,6 +46,8 @@ class GatedSiluMLP(FeedForward):
 @register("ffn", "gated_gelu")
 class GatedGeluMLP(FeedForward):
     graph_safe = True
+    takes_scaled_rows = True      # x may be ScaledRows: the first product finishes the norm
+    defers_output = True          # forward(..., defer=True) may hand the last product on unrun
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -54,12 +56,15 @@ class GatedGeluMLP(FeedForward):
         H, I = self.hidden_size, self.intermediate_size
         return {"gate_up.weight": ParamSpec((2 * I, H), rows=(I, I)), "down.weight": ParamSpec((H, I))}
 
-    def forward(self, x, step):
+    def forward(self, x, step, defer=False):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
         f = gated_linear(x, self.w_gate_up_weight, ws.get("ffn.act", (T, self.intermediate_size), dt),
                          lambda m, n: ws.get("ffn.gate_up", (m, n), dt), act="gelu_tanh")
-        return linear(f, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))
+        out = ws.get("ffn.out", (T, self.hidden_size), dt)
+        if defer and may_defer(f, self.w_down_weight):
+            return PendingProduct(f, self.w_down_weight, None, out)
+        return linear(f, self.w_down_weight, None, out)
 
 
 @register("ffn", "dense_xielu")

@@ -35,13 +35,14 @@ class RMSNorm(Norm):
 
     def add_norm(self, residual, delta, tag, rows=None, n_rows=None, scaled_ok=False, delta_scale=1.0):
         """delta_scale: what is added to the residual is delta_scale * delta (a design whose sub-blocks enter the
-        residual stream times a constant); the product epilogue has no such factor, so nothing is folded then."""
+        residual stream times a constant); the product's residual epilogue takes the factor too."""
         if isinstance(delta, PendingProduct):
-            if scaled_ok and rows is None and delta_scale == 1.0 and self._folds(residual, delta):
+            if scaled_ok and rows is None and self._folds(residual, delta):
                 M, ws = residual.shape[0], self.rt.workspace
                 xw = ws.get(tag + ".scaled", (M, self.size), torch.bfloat16)
                 ssq = ws.get(tag + ".ssq", (native.gemm_rows_grid(), 16), torch.float32)
-                native.gemm_rows(delta.x, delta.weight, residual=residual, norm_w=self.w_weight, xout=xw, ssq_out=ssq)
+                native.gemm_rows(delta.x, delta.weight, residual=residual, norm_w=self.w_weight, xout=xw, ssq_out=ssq,
+                                 res_scale=delta_scale)
                 return ScaledRows(xw, ssq, self.size, self.eps)
             delta = delta.run()
         n = residual.shape[0] if rows is None else (rows.numel() if n_rows is None else n_rows)

@@ -19,7 +19,7 @@ import torch
 
 from .. import native
 from .base import Mixer
-from .linear import linear
+from .linear import PendingProduct, linear, may_defer
 from .registry import register
 from .spec import CacheEntry, CacheNeed, ParamSpec
 
@@ -27,6 +27,8 @@ from .spec import CacheEntry, CacheNeed, ParamSpec
 @register("mixer", "rglru")
 class GatedLinearRecurrence(Mixer):
     graph_safe = True
+    takes_scaled_rows = True      # x may be ScaledRows: the branches' product finishes the norm
+    defers_output = True          # forward(..., defer=True) may hand the output projection on unrun
 
     def __init__(self, hidden_size: int, width: int, blocks: int, taps: int, decay: float = 8.0):
         if width % blocks:
@@ -55,7 +57,7 @@ class GatedLinearRecurrence(Mixer):
             CacheEntry("h", (self.width,), "float32"),
             CacheEntry("conv", (max(self.taps - 1, 1), self.width), "compute")))
 
-    def forward(self, x, step, cache, writes_cache):
+    def forward(self, x, step, cache, writes_cache, defer=False):
         T = x.shape[0]
         W, B = self.width, self.blocks
         bw = W // B
@@ -72,4 +74,7 @@ class GatedLinearRecurrence(Mixer):
         native.rglru_scan(out, gates, self.w_gates_bias, self.w_lam, u, yp, xp, self.w_y_bias, self.w_x_bias,
                           cache.states["h"], conv_state, step.cu_q, step.state_slots, step.num_seqs, self.taps,
                           self.decay, writes_cache)
-        return linear(out, self.w_o_weight, None, ws.get("rg.out", (T, self.hidden_size), dt))
+        res = ws.get("rg.out", (T, self.hidden_size), dt)
+        if defer and may_defer(out, self.w_o_weight):
+            return PendingProduct(out, self.w_o_weight, None, res)
+        return linear(out, self.w_o_weight, None, res)
