@@ -752,6 +752,26 @@ def test_gemm_rows_norm_without_a_pass_of_its_own(native, M, H, I, wdtype):
                                rtol=2e-2, atol=2e-2 * math.sqrt(H / 96))
 
 
+@pytest.mark.parametrize("M,H,I,scale", [(8, 2048, 1024, 0.3), (3, 256, 192, 2.5), (16, 512, 64, 0.0)])
+def test_gemm_rows_residual_times_a_constant(native, M, H, I, scale):
+    """The residual epilogue with a factor: r += scale * (a Wo^T), exact in 32-bit, with the scaled rows and the sums
+    of squares of the new r."""
+    G = native.gemm_rows_grid()
+    a = _rand((M, I), torch.bfloat16, 70)
+    wo = _rand((H, I), torch.bfloat16, 71, I ** -0.5)
+    res0 = _rand((M, H), torch.float32, 72)
+    nw = _rand((H,), torch.float32, 73) * 0.2 + 1
+    res = res0.clone()
+    xw = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ssq = torch.full((G, 16), float("nan"), dtype=torch.float32, device=DEV)
+    native.gemm_rows(a, wo, residual=res, norm_w=nw, xout=xw, ssq_out=ssq, res_scale=scale)
+    native.check_error_flags()
+    r = res0.double() + scale * (a.double() @ wo.double().T)
+    torch.testing.assert_close(res.double(), r, rtol=1e-5, atol=2e-5 * math.sqrt(I / 96))
+    torch.testing.assert_close(ssq[:, :M].double().sum(0), res.double().pow(2).sum(-1), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(xw.double(), (res.double() * nw.double()).bfloat16().double(), rtol=1e-2, atol=1e-2)
+
+
 def test_gemm_rows_refuses_other_sizes(native):
     assert not native.gemm_rows_supports(17, 64, 64, 64)
     assert not native.gemm_rows_supports(4, 64, 96, 96)      # K no multiple of 64
